@@ -1,0 +1,294 @@
+"""Headline benchmark: DeepSeek-V3-size chunked expert-parallel MoE layer, forward + backward.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
+        bench.py --gpus 8 --steps 5 --warmup 3
+
+Config (per rank): T=8192 tokens (seq 4096 x micro-batch 2), D=7168, F=2048, 256 routed experts
+(256/N per GPU), top-8 of sigmoid(logits ~ N(0,1)) normalised over the chosen 8, S=8192, stripe 64,
+bf16, weights ~ N(0, 0.006), synthetic seeded inputs. Weak scaling: per-GPU tokens are fixed.
+
+One step = one forward + one backward of the layer through `chunked_moe` (gradients for x, router
+weights, w_up, w_down). Rank 0 prints ONE JSON line. `value` is tokens/s summed over all GPUs from
+the device-timed loop (CUDA events, max over ranks); `e2e` is the same step driven through the
+public API with the step's inputs copied from pinned host memory and the loss read back every
+step. `--impl baseline` runs the in-repo NCCL all_to_all + library grouped-GEMM layer;
+`--impl reference` is the reference's own JAX build, which cannot be installed offline here.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+CONFIGS = {
+    # name: tokens/rank, D, F, E, K, S, stripe, weight std
+    "dsv3": dict(tokens=8192, hidden=7168, ffn=2048, experts=256, top_k=8, slice_size=8192, stripe=64, std=0.006),
+    "tiny": dict(tokens=16384, hidden=1024, ffn=512, experts=64, top_k=6, slice_size=8192, stripe=64, std=0.02),
+    "smoke": dict(tokens=1024, hidden=512, ffn=256, experts=16, top_k=4, slice_size=1024, stripe=64, std=0.02),
+}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="fused", choices=["fused", "baseline", "reference"])
+    ap.add_argument("--config", default="dsv3", choices=sorted(CONFIGS))
+    ap.add_argument("--comm-dtype", default=None, choices=[None, "float8_e4m3fn"])
+    ap.add_argument("--slice-size", type=int, default=None)
+    ap.add_argument("--skew", default="none", choices=["none", "zipf", "expert0"])
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def reference_unavailable():
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "the reference is a JAX package (hatchling build backend, jax>=0.11.1); neither hatchling nor "
+                       "jax is in the image or the offline wheelhouse, so it can be neither installed nor imported",
+    }))
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs (read-only queries)."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.path = tempfile.NamedTemporaryFile(prefix="clocks_", suffix=".csv", delete=False).name
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu_index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    smax = float(parts[2])
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def make_routing(gen, tokens, experts, top_k, skew, device):
+    import torch
+
+    logits = torch.randn(tokens, experts, generator=gen, device=device)
+    if skew == "zipf":  # Zipf(s=1.2) popularity over experts, sampled without replacement per token
+        pop = 1.0 / torch.arange(1, experts + 1, device=device, dtype=torch.float32) ** 1.2
+        ids = torch.multinomial(pop.expand(tokens, experts), top_k, replacement=False, generator=gen)
+        scores = torch.sigmoid(torch.gather(logits, 1, ids))
+    else:
+        if skew == "expert0":  # adversarial: every token's first choice is expert 0
+            logits[:, 0] += 100.0
+        scores, ids = torch.topk(torch.sigmoid(logits), top_k, dim=-1)
+    weights = scores / scores.sum(-1, keepdim=True)
+    return ids.to(torch.int32), weights.float()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        reference_unavailable()
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from chunked_ep_moe_b200 import ChunkedMoEConfig, chunked_moe
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run for N > 1")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    group = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+
+    c = dict(CONFIGS[args.config])
+    if args.slice_size:
+        c["slice_size"] = args.slice_size
+    T, D, F, E, K, S = c["tokens"], c["hidden"], c["ffn"], c["experts"], c["top_k"], c["slice_size"]
+    L = E // world
+    fused = args.impl == "fused"
+    cfg = ChunkedMoEConfig(num_experts=E, top_k=K, slice_size=S, stripe_width=c["stripe"],
+                           transport="nvshmem" if fused else "ragged_a2a",
+                           expert_compute="fused" if fused else "reference", comm_dtype=args.comm_dtype)
+
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    w_up = torch.empty(L, D, 2 * F, device=dev, dtype=torch.bfloat16)
+    w_down = torch.empty(L, F, D, device=dev, dtype=torch.bfloat16)
+    for l in range(L):  # per expert: no 30 GB fp32 temporary at L=256
+        w_up[l] = (torch.randn(D, 2 * F, generator=gen, device=dev) * c["std"]).to(torch.bfloat16)
+        w_down[l] = (torch.randn(F, D, generator=gen, device=dev) * c["std"]).to(torch.bfloat16)
+    w_up.requires_grad_(True)
+    w_down.requires_grad_(True)
+
+    # Host-side step inputs in pinned memory (the end-to-end loop copies them in every step).
+    ids_d, weights_d = make_routing(gen, T, E, K, args.skew, dev)
+    x_h = torch.randn(T, D, generator=torch.Generator().manual_seed(99 + rank)).to(torch.bfloat16).pin_memory()
+    g_d = torch.randn(T, D, generator=gen, device=dev).to(torch.bfloat16)
+    ids_h, weights_h = ids_d.cpu().pin_memory(), weights_d.cpu().pin_memory()
+    loss_h = torch.zeros(1, dtype=torch.float32).pin_memory()
+    x_d = x_h.to(dev)
+
+    def step(x, ids, weights):
+        x = x.requires_grad_(True)
+        weights = weights.requires_grad_(True)
+        w_up.grad = None
+        w_down.grad = None
+        out = chunked_moe(x, ids, weights, w_up, w_down, cfg, group)
+        out.backward(g_d)
+        return out, x.grad, weights.grad
+
+    def step_e2e():
+        x = x_h.to(dev, non_blocking=True)
+        ids = ids_h.to(dev, non_blocking=True)
+        weights = weights_h.to(dev, non_blocking=True)
+        out, dx, dw = step(x, ids, weights)
+        loss_h.copy_((out.float().mean() + dx.float().mean()).reshape(1), non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the host owns the step's result before the next step starts
+        return float(loss_h[0])
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier(group=group)
+            torch.cuda.synchronize()
+
+    def launches():
+        if not fused:
+            return 0
+        from chunked_ep_moe_b200.ops import fused as fused_mod
+
+        return fused_mod.launches()
+
+    for _ in range(max(args.warmup, 3)):
+        step(x_d.clone(), ids_d, weights_d.clone())
+    sync_all()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    l0 = launches()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    start.record()
+    for _ in range(args.steps):
+        step(x_d.detach(), ids_d, weights_d.detach())
+    stop.record()
+    sync_all()
+    ms = start.elapsed_time(stop) / args.steps
+    n_launch = (launches() - l0) // max(args.steps, 1)
+
+    e2e = None
+    if not args.no_e2e:
+        step_e2e()
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step_e2e()
+        e1.record()
+        sync_all()
+        e2e_ms = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop()
+
+    t = torch.tensor([ms, e2e_ms if not args.no_e2e else 0.0], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    ms, e2e_ms = float(t[0]), float(t[1])
+    if not args.no_e2e:
+        h2d = x_h.numel() * 2 + ids_h.numel() * 4 + weights_h.numel() * 4
+        e2e = {"value": world * T / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4}
+
+    if rank == 0:
+        flops = 24.0 * D * F * T * K  # per rank, fwd + bwd with full remat
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(REPO, "MEASURED_PEAKS.json")))
+        except OSError:
+            pass
+        peak = peaks.get("bf16_tflops_sustained", 1400.0)
+        result = {
+            "metric": "moe_layer_fwd_bwd_tokens_per_s",
+            "value": world * T / (ms / 1e3),
+            "unit": "tokens/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": max(args.warmup, 3),
+            "ms_per_step": ms,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "bf16",
+            "data": "synthetic (seeded N(0,1) tokens, random-init N(0,%g) weights, top-%d of sigmoid logits)" % (c["std"], K),
+            "impl": args.impl,
+            "tokens_per_s_per_gpu": T / (ms / 1e3),
+            "tflops_per_gpu": flops / (ms / 1e3) / 1e12,
+            "frac_of_measured_sustained_bf16_peak": flops / (ms / 1e3) / 1e12 / peak,
+            "config": {"model": "DeepSeek-V3-size MoE layer" if args.config == "dsv3" else args.config,
+                       "tokens_per_rank": T, "global_batch": world * T, "seq_len": 4096, "hidden": D, "ffn": F,
+                       "experts": E, "experts_per_gpu": L, "top_k": K, "slice_size": S, "stripe_width": c["stripe"],
+                       "comm_dtype": args.comm_dtype or "bf16", "skew": args.skew,
+                       "parallelism": f"ep{world}",
+                       "l2": "inputs larger than L2: %.1f GB of expert weights stream through every step"
+                             % ((w_up.numel() + w_down.numel()) * 2 / 1e9)},
+            "clocks": clocks,
+            "e2e": e2e,
+            "gpu_launches": int(n_launch),
+        }
+        print(json.dumps(result))
+    if world > 1:
+        dist.barrier(group=group)
+        from chunked_ep_moe_b200.ops import fused as fused_mod
+
+        fused_mod.release_workspaces()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,97 @@
+"""Builds and loads the in-tree sm_100a extension (`chunked_ep_moe_b200/_C*.so`).
+
+The extension is compiled for sm_100a only (`-gencode arch=compute_100a,code=sm_100a`) with ninja
+through `torch.utils.cpp_extension`, into `chunked_ep_moe_b200/_ext/`, and the resulting shared
+object is imported from there. nvcc cross-compiles without a GPU, so `build()` works on a CPU-only
+machine; loading the module needs no GPU either (the CPU plan builder lives in it).
+"""
+
+from __future__ import annotations
+
+import importlib.util
+import os
+import sys
+import threading
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+_CSRC = os.path.join(_PKG_DIR, "csrc")
+_BUILD_DIR = os.path.join(_PKG_DIR, "_ext")
+_NAME = "chunked_ep_moe_b200_C"
+_SOURCES = [
+    "bindings.cpp",
+    "runtime/tensor_map.cpp",
+    "runtime/fused_rank.cpp",
+    "gemm/grouped_gemm.cu",
+    "comm/comm_kernels.cu",
+    "plan/plan_kernel.cu",
+]
+_lock = threading.Lock()
+_module = None
+
+
+def _sources() -> list[str]:
+    out = []
+    for rel in _SOURCES:
+        path = os.path.join(_CSRC, rel)
+        if os.path.exists(path) and os.path.splitext(path)[1] in (".cpp", ".cu"):
+            out.append(path)
+    return out
+
+
+def _so_path() -> str:
+    return os.path.join(_BUILD_DIR, _NAME + ".so")
+
+
+def _is_stale() -> bool:
+    so = _so_path()
+    if not os.path.exists(so):
+        return True
+    built = os.path.getmtime(so)
+    for root, _, files in os.walk(_CSRC):
+        for f in files:
+            if os.path.getmtime(os.path.join(root, f)) > built:
+                return True
+    return False
+
+
+def build(verbose: bool = False, force: bool = False):
+    """Compiles the extension if its sources are newer than the built object; returns the module."""
+    global _module
+    with _lock:
+        if _module is not None and not force:
+            return _module
+        if force or _is_stale():
+            if os.environ.get("CEM_NO_BUILD") == "1":
+                raise RuntimeError("the sm_100a extension is missing or stale and CEM_NO_BUILD=1 forbids building it")
+            from torch.utils.cpp_extension import load
+
+            os.makedirs(_BUILD_DIR, exist_ok=True)
+            os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
+            load(
+                name=_NAME,
+                sources=_sources(),
+                extra_cflags=["-O3", "-std=c++17"],
+                extra_cuda_cflags=["-O3", "-std=c++17", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
+                                   "--expt-relaxed-constexpr"],
+                extra_include_paths=[_CSRC],
+                build_directory=_BUILD_DIR,
+                verbose=verbose,
+                is_python_module=False,
+            )
+        spec = importlib.util.spec_from_file_location(_NAME, _so_path())
+        module = importlib.util.module_from_spec(spec)
+        import torch  # noqa: F401  (libtorch must be loaded before the extension)
+
+        spec.loader.exec_module(module)
+        sys.modules[_NAME] = module
+        _module = module
+        return module
+
+
+def load():
+    """Returns the extension, building it first when needed. Raises if it cannot be had."""
+    return build()
+
+
+def is_built() -> bool:
+    return os.path.exists(_so_path())

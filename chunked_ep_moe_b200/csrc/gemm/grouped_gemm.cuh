@@ -1,0 +1,77 @@
+// Parameters of the grouped tcgen05 GEMM engine (one persistent kernel, six epilogues).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "../common/status.cuh"
+#include "../plan/plan_tables.cuh"
+
+namespace cem {
+
+// Tile shape of every mode: 128 x 256 accumulator (fp32 in TMEM, double buffered = all 512
+// columns), K step 64 bf16 = one 128-byte swizzle span, 4-stage TMA pipeline.
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 256;
+constexpr int kBlockK = 64;
+constexpr int kStages = 4;
+constexpr int kUmmaK = 16;
+constexpr int kGemmThreads = 192;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
+constexpr int kRasterBand = 8;     // row tiles swept together across N so their A rows stay in L2
+
+enum GemmMode : int {
+  kModeSwiglu = 0,   // act = silu(x Wg) * (x Wu) from striped w_up; optional h          (replaces gmm_swiglu)
+  kModeDownFwd = 1,  // y = act Wd; epilogue x router weight, rows stored to their source rank (gmm + combine)
+  kModeDownDw = 2,   // backward remat of y: d_weight partials <g, y> and dy = w * g, y never stored
+  kModeDswiglu = 3,  // d_act = dy Wd^T; epilogue SwiGLU' with h -> dh                     (gmm_dswiglu)
+  kModeDx = 4,       // dx = dh Wu^T; rows (+ d_weight scalar) stored to their source rank  (gmm^T + combine)
+  kModeTgmm = 5,     // dW[g] = lhs[rows_g]^T rhs[rows_g], fp32 carry across slices         (tgmm + accumulate)
+};
+
+struct GemmParams {
+  // --- schedule ---------------------------------------------------------------------------
+  const int* plan;   // per-pass plan buffer (see plan_tables.cuh)
+  PlanLayout lay;
+  int slice;         // slice index inside the pass
+  int n_tiles;       // N / 256
+  int m_tiles;       // tgmm: M / 128 (row tiles of the weight gradient); unused otherwise
+  int k_blocks;      // gmm modes: K / 64
+  int b_group_rows;  // rows one expert occupies in the flattened 2-D weight tensor map
+  int me;            // this rank
+  int stripe;        // SwiGLU stripe width (swiglu / dswiglu)
+  uint32_t spin_limit;
+  uint32_t mbar_limit;
+  StatusBlock* status;
+  // --- arrival flags (swiglu consumer) -----------------------------------------------------
+  const uint32_t* arrive;     // [P*L] cumulative rows received per (source, local expert); null = no wait
+  const uint32_t* pass_base;  // [P*L] value of `arrive` when this pass began
+  // --- row-wise outputs / inputs (leading dims in elements) -----------------------------------
+  __nv_bfloat16* out0;        // swiglu: act [S,F]; down_dw: dy [S,D]; dswiglu: dh [S,2F]
+  __nv_bfloat16* out1;        // swiglu: h [S,2F] or null
+  const __nv_bfloat16* in0;   // down_dw: g [S,D]; dswiglu: h [S,2F]
+  const float* row_w;         // down_fwd / down_dw: router weight per slice row [S]
+  float* dwp;                 // down_dw: out [S, n_tiles]; dx: in [S, dwp_tiles]
+  int dwp_tiles;
+  int ld0, ld1;
+  // --- combine targets (down_fwd, dx) --------------------------------------------------------
+  __nv_bfloat16* const* peer_rows;   // [P] base of each source rank's [T*K, ld] return buffer
+  float* const* peer_dw;             // [P] base of each source rank's [T*K] d_weight rows (dx only)
+  uint32_t* const* peer_count;       // [P] each source rank's returned-row counter
+  // --- tgmm ---------------------------------------------------------------------------------
+  const float* carry_in;   // [M, N] fp32 partial of the expert that straddles the previous slice boundary
+  float* carry_out;        // [M, N] fp32 partial of the expert that straddles the next slice boundary
+  __nv_bfloat16* grad_out; // [L, M, N] final gradient
+};
+
+// Dynamic shared memory the kernel asks for.
+constexpr int kStageBytesA = kBlockM * kBlockK * 2;
+constexpr int kStageBytesB = kBlockN * kBlockK * 2;
+constexpr int kStageBytes = kStageBytesA + kStageBytesB;
+constexpr int kStagingBytes = 4 * 32 * 256;  // per epilogue warp: 32 rows x 128 bf16 columns
+constexpr int kGemmSmemBytes = 1024 /*alignment slack*/ + kStages * kStageBytes + kStagingBytes + 256 /*barriers*/;
+
+void launch_grouped_gemm(int mode, const GemmParams& p, const CUtensorMap& map_a, const CUtensorMap& map_b, int grid,
+                         cudaStream_t stream);
+
+}  // namespace cem

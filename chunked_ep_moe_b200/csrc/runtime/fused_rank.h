@@ -1,0 +1,119 @@
+// Per-rank executor of the fused NVLink path: owns the scratch buffers, the peer pointer tables,
+// the TMA descriptors, the comm stream and the slice sequence counter, and launches the kernels
+// of one slice at a time.
+//
+// The step methods (begin_*, put, compute_*, finish_*) are what a pass is made of:
+//
+//     begin_forward -> put(0) -> for j: put(j+1); compute_forward(j) -> finish_forward
+//
+// One process drives one rank per GPU that way. A test harness may instead drive several
+// ranks that live on ONE device in lockstep (all puts of a slice, then all computes); then
+// every flag a kernel looks at has already been set when it starts and nothing ever spins.
+#pragma once
+
+#include <torch/extension.h>
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../comm/comm_kernels.cuh"
+#include "../gemm/grouped_gemm.cuh"
+#include "../plan/plan_kernel.cuh"
+
+namespace cem {
+
+// Byte offsets inside one rank's symmetric arena (identical on every rank).
+struct ArenaLayout {
+  size_t xbuf, gbuf, wbuf, xq, gq, xs, gs, ret, dw_rows, arrive, credit, ret_count, traffic, traffic_flags, total;
+};
+
+ArenaLayout make_arena_layout(int P, int L, int S, int D, int tk_cap, bool fp8);
+
+class FusedRank {
+ public:
+  FusedRank(int P, int L, int me, int S, int D, int F, int K, int stripe, int tk_cap, int max_slices, int num_sms,
+            bool fp8, int64_t arena, std::vector<int64_t> peer_arenas, bool use_comm_stream, int64_t spin_limit,
+            int put_blocks);
+  ~FusedRank();
+
+  // Forward pass set-up: sort, traffic exchange, plan tables, arrival targets. `plan`, `order`,
+  // `inv_order` are caller-owned int32 tensors (they are what the backward needs again).
+  // With `counts_prefilled` the [P,P,L] traffic matrix in `counts` is taken as is (lockstep harness).
+  // Returns the number of slices (this synchronises the host with the plan kernel once).
+  int64_t begin_forward(torch::Tensor expert_ids, torch::Tensor plan, torch::Tensor order, torch::Tensor inv_order,
+                        torch::Tensor counts, bool counts_prefilled);
+  // Lockstep harness only: sort + histogram without the exchange (fills order, inv_order, my row of counts).
+  void sort_only(torch::Tensor expert_ids, torch::Tensor order, torch::Tensor inv_order, torch::Tensor my_counts);
+  int64_t begin_backward(torch::Tensor plan);
+
+  void put(int64_t j, torch::Tensor plan, torch::Tensor order, torch::Tensor x, c10::optional<torch::Tensor> g,
+           torch::Tensor w_flat);
+  void compute_forward(int64_t j, torch::Tensor plan, torch::Tensor w_up, torch::Tensor w_down);
+  void compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_up, torch::Tensor w_down, torch::Tensor dw_up,
+                        torch::Tensor dw_down);
+  void finish_forward(torch::Tensor inv_order, torch::Tensor out);
+  void finish_backward(torch::Tensor inv_order, torch::Tensor dx, torch::Tensor d_weights);
+
+  // Reads the status block (synchronises); throws std::runtime_error describing the first recorded error.
+  void check_status();
+  std::vector<int64_t> plan_header() const { return std::vector<int64_t>(host_header_, host_header_ + 16); }
+  int64_t plan_ints() const { return lay_.total; }
+  int64_t launches() const { return launches_; }
+  // Debug views of the local scratch (tests compare them with the torch reference).
+  torch::Tensor act() const { return act_; }
+  torch::Tensor h() const { return h_; }
+  torch::Tensor dh() const { return dh_; }
+  torch::Tensor dy() const { return dy_; }
+
+ private:
+  void end_pass(int64_t n_slices);
+  GemmParams base_params(const int* plan, int j) const;
+  const CUtensorMap& weight_map(const torch::Tensor& w, uint32_t box_rows);
+  void launch_gemm(int mode, const GemmParams& p, const CUtensorMap& a, const CUtensorMap& b, cudaStream_t st);
+
+  int P_, L_, me_, S_, D_, F_, K_, stripe_, tk_cap_, max_slices_, num_sms_, put_blocks_;
+  bool fp8_, use_comm_stream_;
+  uint32_t spin_limit_, mbar_limit_;
+  PlanLayout lay_;
+  ArenaLayout arena_lay_;
+  uint8_t* arena_;
+  std::vector<uint8_t*> peers_;
+
+  // local scratch (torch-owned)
+  torch::Tensor act_, h_, dy_, dh_, dwp_, carry_up_, carry_down_, pass_base_, expected_total_, status_, tables_,
+      sort_scratch_, my_counts_;
+  // device pointer tables, rows of `tables_`
+  enum Table { kTabX, kTabG, kTabW, kTabXq, kTabGq, kTabXs, kTabGs, kTabArrive, kTabRet, kTabDw, kTabCount,
+               kTabCredit, kTabTraffic0, kTabTraffic1, kTabTflags0, kTabTflags1, kNumTables };
+  template <typename T>
+  T* const* table(int t) const { return reinterpret_cast<T* const*>(tables_.data_ptr<int64_t>() + t * P_); }
+
+  CUtensorMap map_x_k_[2], map_x_mn_[2], map_act_k_, map_act_mn_, map_dy_k_, map_dy_mn_, map_dh_k_, map_dh_mn_;
+  std::map<std::pair<const void*, uint32_t>, CUtensorMap> weight_maps_;
+
+  cudaStream_t comm_stream_ = nullptr;
+  cudaEvent_t ev_pass_ = nullptr, ev_put_[4] = {}, ev_done_[4] = {};
+  int32_t* host_header_ = nullptr;  // pinned: 16 plan header ints + 8 status ints
+
+  uint32_t seq_ = 0;          // global slice sequence number of the next pass's first slice
+  uint32_t fwd_epoch_ = 0;    // forward passes started (traffic exchange epoch)
+  uint32_t ret_target_ = 0;   // value the returned-row counter reaches at the end of the current pass
+  int64_t cur_slices_ = 0;
+  int64_t cur_rows_ = 0;      // T*K of the current pass
+  int64_t launches_ = 0;
+};
+
+// Symmetric arena helpers (cudaMalloc + CUDA IPC), one arena per rank.
+int64_t arena_alloc(int64_t bytes);
+void arena_free(int64_t ptr);
+py::bytes arena_export(int64_t ptr);
+int64_t arena_import(py::bytes handle);
+void arena_close(int64_t ptr);
+void arena_zero(int64_t ptr, int64_t bytes);
+void arena_fill(int64_t ptr, int64_t bytes, int value);
+
+}  // namespace cem

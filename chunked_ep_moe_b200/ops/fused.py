@@ -1,0 +1,155 @@
+"""The fused NVLink path: `chunked_moe` on the sm_100a kernels (`transport="nvshmem"`, `expert_compute="fused"`).
+
+Per pass the host launches, per slice, a put kernel on the comm stream and a handful of grouped
+tcgen05 GEMMs on the compute stream; everything between ranks happens inside those kernels
+(peer stores, arrival counters, credits). Compared with the reference's loop
+(src/chunked_moe/moe.py:96-119, :148-206):
+
+  * no `[T*K, D]` send buffer: the put kernel gathers rows straight from `x[token]`;
+  * the router weight is applied in the down-projection epilogue, which stores every finished
+    row into the source rank's return buffer; a local K-way fixed-order sum finishes the token;
+  * the backward folds `y` into `d_weight = <g, y>` inside the recomputed down GEMM's epilogue
+    and forms `dy = w * g` there, so `y` never reaches HBM;
+  * weight gradients are written once per expert in bf16; only the (at most one) expert that
+    straddles a slice boundary carries an fp32 partial to the next slice.
+
+Only the inputs and the integer plan (tables, send order, its inverse) are kept for the backward.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _build
+from ..config import ChunkedMoEConfig
+from ..parallel.symm import SymmetricArena
+
+_DEFAULT_SPIN_LIMIT = 1 << 24  # polls (~0.3 us each) before a wait on another rank gives up
+_PUT_BLOCKS = 32
+
+_workspaces: dict = {}
+
+
+class FusedWorkspace:
+    """Symmetric arena + per-rank executor for one (geometry, process group)."""
+
+    def __init__(self, cfg: ChunkedMoEConfig, group, hidden: int, ffn: int, tk_cap: int):
+        ext = _build.load()
+        initialised = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if initialised else 1
+        self.rank_index = dist.get_rank(group) if initialised else 0
+        self.local_experts = cfg.num_experts // self.world
+        if self.world > 1:  # the arena layout must be identical everywhere: agree on the capacity
+            cap = torch.tensor([tk_cap], device="cuda", dtype=torch.int64)
+            dist.all_reduce(cap, op=dist.ReduceOp.MAX, group=group)
+            tk_cap = int(cap.item())
+        self.tk_cap = tk_cap
+        self.fp8 = cfg.comm_dtype == "float8_e4m3fn"
+        self.max_slices = max(1, math.ceil(self.world * tk_cap / cfg.slice_size)) + 1
+        nbytes = ext.arena_bytes(self.world, self.local_experts, cfg.slice_size, hidden, tk_cap, self.fp8)
+        self.arena = SymmetricArena(nbytes, group)
+        self.rank = ext.FusedRank(
+            P=self.world, L=self.local_experts, me=self.rank_index, S=cfg.slice_size, D=hidden, F=ffn, K=cfg.top_k,
+            stripe=cfg.stripe_width, tk_cap=tk_cap, max_slices=self.max_slices, num_sms=cfg.num_sms, fp8=self.fp8,
+            arena=self.arena.local, peer_arenas=self.arena.peers, use_comm_stream=True,
+            spin_limit=_DEFAULT_SPIN_LIMIT, put_blocks=_PUT_BLOCKS)
+        self.plan_ints = self.rank.plan_ints()
+        self.dummy_counts = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+
+def get_workspace(cfg: ChunkedMoEConfig, group, hidden: int, ffn: int, tokens_times_k: int) -> FusedWorkspace:
+    key = (id(group) if group is not None else 0, cfg.num_experts, cfg.top_k, cfg.slice_size, cfg.stripe_width,
+           cfg.comm_dtype, cfg.num_sms, hidden, ffn, torch.cuda.current_device())
+    ws = _workspaces.get(key)
+    if ws is None or ws.tk_cap < tokens_times_k:
+        if ws is not None:
+            ws.arena.close()
+        ws = FusedWorkspace(cfg, group, hidden, ffn, tokens_times_k)
+        _workspaces[key] = ws
+    return ws
+
+
+def release_workspaces() -> None:
+    """Frees every cached workspace (collective when a process group is involved)."""
+    for ws in list(_workspaces.values()):
+        ws.rank = None
+        ws.arena.close()
+    _workspaces.clear()
+
+
+def launches() -> int:
+    """Kernels launched so far by every cached workspace of this process."""
+    return sum(int(ws.rank.launches()) for ws in _workspaces.values() if ws.rank is not None)
+
+
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise ValueError("chunked_moe fused path: " + msg)
+
+
+class _ChunkedMoEFused(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, expert_ids, weights, w_up, w_down, cfg, group):
+        tokens, hidden = x.shape
+        ffn = w_down.shape[1]
+        ws = get_workspace(cfg, group, hidden, ffn, tokens * cfg.top_k)
+        rank = ws.rank
+        dev = x.device
+        plan = torch.empty(ws.plan_ints, dtype=torch.int32, device=dev)
+        order = torch.empty(tokens * cfg.top_k, dtype=torch.int32, device=dev)
+        inv_order = torch.empty_like(order)
+        ids32 = expert_ids.to(torch.int32).contiguous()
+        w_flat = weights.detach().float().reshape(-1).contiguous()
+        xc, w_up_c, w_down_c = x.detach().contiguous(), w_up.detach().contiguous(), w_down.detach().contiguous()
+        n = rank.begin_forward(ids32, plan, order, inv_order, ws.dummy_counts, False)
+        out = torch.empty_like(xc)
+        if n > 0:
+            rank.put(0, plan, order, xc, None, w_flat)
+        for j in range(n):
+            if j + 1 < n:
+                rank.put(j + 1, plan, order, xc, None, w_flat)  # slice j+1 is in flight while slice j computes
+            rank.compute_forward(j, plan, w_up_c, w_down_c)
+        rank.finish_forward(inv_order, out)
+        ctx.save_for_backward(xc, weights, w_up_c, w_down_c, plan, order, inv_order)
+        ctx.cfg, ctx.group, ctx.ws = cfg, group, ws
+        ctx.mark_non_differentiable(expert_ids)
+        return out
+
+    @staticmethod
+    def backward(ctx, g_out):
+        x, weights, w_up, w_down, plan, order, inv_order = ctx.saved_tensors
+        rank = ctx.ws.rank
+        g = g_out.to(x.dtype).contiguous()
+        w_flat = weights.detach().float().reshape(-1).contiguous()
+        n = rank.begin_backward(plan)
+        dw_up, dw_down = torch.empty_like(w_up), torch.empty_like(w_down)
+        if n > 0:
+            rank.put(0, plan, order, x, g, w_flat)
+        else:
+            dw_up.zero_()
+            dw_down.zero_()
+        for j in range(n):
+            if j + 1 < n:
+                rank.put(j + 1, plan, order, x, g, w_flat)
+            rank.compute_backward(j, plan, w_up, w_down, dw_up, dw_down)
+        dx = torch.empty_like(x)
+        d_weights = torch.empty(weights.numel(), dtype=torch.float32, device=x.device)
+        rank.finish_backward(inv_order, dx, d_weights)
+        return dx, None, d_weights.reshape(weights.shape).to(weights.dtype), dw_up, dw_down, None, None
+
+
+def chunked_moe_fused(x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Tensor, w_up: torch.Tensor,
+                      w_down: torch.Tensor, cfg: ChunkedMoEConfig,
+                      group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    _require(cfg.expert_compute == "fused", 'transport="nvshmem" requires expert_compute="fused"')
+    _require(x.is_cuda, "inputs must be CUDA tensors (the sm_100a extension has no CPU path)")
+    _require(x.dtype == torch.bfloat16 and w_up.dtype == torch.bfloat16 and w_down.dtype == torch.bfloat16,
+             "x, w_up and w_down must be bfloat16")
+    _require(x.shape[1] % 256 == 0 and w_down.shape[1] % 256 == 0, "needs D % 256 == 0 and F % 256 == 0")
+    _require(cfg.stripe_width in (32, 64, 128), "needs stripe_width in {32, 64, 128}")
+    _require(cfg.slice_size % 8 == 0, "needs slice_size % 8 == 0")
+    return _ChunkedMoEFused.apply(x, expert_ids, weights, w_up, w_down, cfg, group)

@@ -1,0 +1,186 @@
+"""Fused sm_100a path on a real GPU vs plain-PyTorch fp32 references of the same ops.
+
+Follows the reference's kernel-test strategy (tests/test_fused_kernels.py:18-67): partial slices,
+an empty expert, a one-row expert, NaN-poisoned padding, bf16 tolerance 3e-2 x max-abs; plus the
+layer grid of tests/test_moe.py run through the single-device lockstep harness for P > 1.
+"""
+
+import math
+
+import pytest
+import torch
+
+from chunked_ep_moe_b200 import ChunkedMoEConfig, chunked_moe, stripe_weights
+from chunked_ep_moe_b200.ops import plan as plan_lib
+
+import moe_cases
+
+pytestmark = pytest.mark.gpu
+
+TOL = 3e-2
+
+
+def _close(got, want, name, tol=TOL):
+    got, want = got.float(), want.float()
+    assert torch.isfinite(got).all(), f"{name}: non-finite values"
+    scale = want.abs().max().clamp_min(1e-6)
+    err = (got - want).abs().max() / scale
+    assert err <= tol, f"{name}: max abs err {err:.4f} x max-abs (allowed {tol})"
+
+
+def _ids_with_groups(group_rows, top_k, num_experts, gen):
+    """Token routing whose per-expert copy counts are exactly `group_rows` (K distinct experts per token not required)."""
+    flat = torch.cat([torch.full((n,), e, dtype=torch.int32) for e, n in enumerate(group_rows)])
+    flat = flat[torch.randperm(flat.numel(), generator=gen)]
+    assert flat.numel() % top_k == 0
+    return flat.reshape(-1, top_k)
+
+
+def _oracle_dev(x, ids, weights, w_up, w_down, g, stripe):
+    return moe_cases.oracle(x.float().cpu(), ids.cpu(), weights.float().cpu(), w_up.float().cpu(),
+                            w_down.float().cpu(), g.float().cpu(), stripe)
+
+
+def test_expert_sort_matches_stable_argsort():
+    from chunked_ep_moe_b200 import _build
+    from chunked_ep_moe_b200.parallel.lockstep import LockstepWorld
+
+    gen = torch.Generator().manual_seed(0)
+    cfg = ChunkedMoEConfig(num_experts=64, top_k=4, slice_size=256, transport="nvshmem", expert_compute="fused",
+                           stripe_width=64)
+    world = LockstepWorld(cfg, 1, 256, 256, 1500)
+    ids = torch.randint(0, 64, (1500, 4), generator=gen, dtype=torch.int32).cuda()
+    order = torch.empty(6000, dtype=torch.int32, device="cuda")
+    inv = torch.empty_like(order)
+    counts = torch.zeros(64, dtype=torch.int32, device="cuda")
+    world.ranks[0].sort_only(ids, order, inv, counts)
+    ref_order, ref_counts = plan_lib.sort_and_count(ids.cpu(), 64)
+    assert torch.equal(order.cpu().long(), ref_order)
+    assert torch.equal(counts.cpu().long(), ref_counts)
+    assert torch.equal(inv.cpu().long()[ref_order], torch.arange(6000))
+    world.close()
+
+
+CASES = [
+    # (group rows per expert, slice size, stripe)
+    ([40, 0, 70, 18], 128, 64),      # partial slice, empty expert
+    ([64, 1, 63, 0], 128, 128),      # full slice, one-row expert, trailing empty expert
+    ([300, 5, 0, 203], 200, 32),     # experts straddling several slices, S not a multiple of 128
+    ([130, 126, 256, 0], 1024, 64),  # one slice larger than the whole stream
+]
+
+
+@pytest.mark.parametrize("group_rows,slice_size,stripe", CASES)
+def test_single_rank_layer_matches_oracle(group_rows, slice_size, stripe):
+    gen = torch.Generator().manual_seed(1)
+    E, K, D, F = len(group_rows), 2, 256, 256
+    ids = _ids_with_groups(group_rows, K, E, gen)
+    T = ids.shape[0]
+    x = torch.randn(T, D, generator=gen)
+    weights = torch.rand(T, K, generator=gen) + 0.1
+    w_gate = torch.randn(E, D, F, generator=gen) / math.sqrt(D)
+    w_upp = torch.randn(E, D, F, generator=gen) / math.sqrt(D)
+    w_down = torch.randn(E, F, D, generator=gen) / math.sqrt(F)
+    g = torch.randn(T, D, generator=gen)
+    w_up = stripe_weights(w_gate, w_upp, stripe)
+
+    cfg = ChunkedMoEConfig(num_experts=E, top_k=K, slice_size=slice_size, transport="nvshmem",
+                           expert_compute="fused", stripe_width=stripe)
+    dev = lambda t: t.cuda().to(torch.bfloat16)
+    xs, us, ds = dev(x).requires_grad_(True), dev(w_up).requires_grad_(True), dev(w_down).requires_grad_(True)
+    ws = weights.cuda().requires_grad_(True)
+    out = chunked_moe(xs, ids.cuda(), ws, us, ds, cfg, None)
+    (out.float() * g.cuda()).sum().backward()
+    torch.cuda.synchronize()
+
+    want = _oracle_dev(xs.detach(), ids, ws.detach(), us.detach(), ds.detach(), dev(g), stripe)
+    _close(out.detach().cpu(), want["out"], "out")
+    _close(xs.grad.cpu(), want["dx"], "dx")
+    _close(ws.grad.cpu(), want["dweights"], "dweights")
+    _close(us.grad.cpu(), want["dw_up"], "dw_up")
+    _close(ds.grad.cpu(), want["dw_down"], "dw_down")
+
+
+def test_nan_poisoned_padding_does_not_leak():
+    """Scratch and slice buffers full of NaN patterns: rows outside a group must never reach an output."""
+    from chunked_ep_moe_b200 import _build
+    from chunked_ep_moe_b200.parallel.lockstep import LockstepWorld
+
+    ext = _build.load()
+    gen = torch.Generator().manual_seed(2)
+    E, K, D, F, S, stripe = 4, 2, 256, 256, 256, 64
+    group_rows = [70, 0, 41, 9]
+    ids = _ids_with_groups(group_rows, K, E, gen)
+    T = ids.shape[0]
+    cfg = ChunkedMoEConfig(num_experts=E, top_k=K, slice_size=S, transport="nvshmem", expert_compute="fused",
+                           stripe_width=stripe)
+    world = LockstepWorld(cfg, 1, D, F, T)
+    lay = ext.arena_layout(1, E, S, D, T * K, False)
+    ext.arena_fill(world.arenas.bases[0] + lay["xbuf"], lay["xq"] - lay["xbuf"], 0xFF)  # x, g, w slice buffers
+    ext.arena_fill(world.arenas.bases[0] + lay["ret"], lay["arrive"] - lay["ret"], 0xFF)
+    rk = world.ranks[0]
+    for t in (rk.act(), rk.h(), rk.dh(), rk.dy()):
+        t.fill_(float("nan"))
+    bf = lambda t: t.cuda().to(torch.bfloat16)
+    x, g = bf(torch.randn(T, D, generator=gen)), bf(torch.randn(T, D, generator=gen))
+    weights = (torch.rand(T, K, generator=gen) + 0.1).cuda()
+    w_up = bf(torch.randn(E, D, 2 * F, generator=gen) / math.sqrt(D))
+    w_down = bf(torch.randn(E, F, D, generator=gen) / math.sqrt(F))
+    outs, saved = world.forward([x], [ids.cuda()], [weights], [w_up], [w_down])
+    dxs, dws, dw_ups, dw_downs = world.backward([x], [g], [w_up], [w_down], saved)
+    torch.cuda.synchronize()
+    want = _oracle_dev(x, ids, weights, w_up, w_down, g, stripe)
+    _close(outs[0].cpu(), want["out"], "out")
+    _close(dxs[0].cpu(), want["dx"], "dx")
+    _close(dws[0].reshape(T, K).cpu(), want["dweights"], "dweights")
+    _close(dw_ups[0].cpu(), want["dw_up"], "dw_up")
+    _close(dw_downs[0].cpu(), want["dw_down"], "dw_down")
+    world.close()
+
+
+@pytest.mark.parametrize("world_size,skew,slice_size", [(2, "uniform", 128), (4, "uniform", 64), (4, "all_one", 64),
+                                                        (4, "rank0", 256), (8, "uniform", 2048)])
+def test_lockstep_multi_rank_matches_oracle(world_size, skew, slice_size):
+    from chunked_ep_moe_b200.parallel.lockstep import LockstepWorld
+
+    T, E, K, D, F, stripe = 48, 16, 4, 256, 256, 64
+    x, ids, weights, w_up, w_down, g = moe_cases.setup(world_size, T, E, K, D, F, skew, seed=3)
+    cfg = ChunkedMoEConfig(num_experts=E, top_k=K, slice_size=slice_size, transport="nvshmem",
+                           expert_compute="fused", stripe_width=stripe)
+    bf = lambda t: t.cuda().to(torch.bfloat16).contiguous()
+    sh = lambda t, r: moe_cases.shard(t, r, world_size)
+    xs = [bf(sh(x, r)) for r in range(world_size)]
+    gs = [bf(sh(g, r)) for r in range(world_size)]
+    idl = [sh(ids, r).cuda() for r in range(world_size)]
+    wl = [sh(weights, r).cuda() for r in range(world_size)]
+    ups = [bf(sh(w_up, r)) for r in range(world_size)]
+    downs = [bf(sh(w_down, r)) for r in range(world_size)]
+    world = LockstepWorld(cfg, world_size, D, F, T)
+    outs, saved = world.forward(xs, idl, wl, ups, downs)
+    dxs, dws, dw_ups, dw_downs = world.backward(xs, gs, ups, downs, saved)
+    torch.cuda.synchronize()
+    want = _oracle_dev(torch.cat(xs), ids, weights, torch.cat(ups), torch.cat(downs), torch.cat(gs), stripe)
+    _close(torch.cat(outs).cpu(), want["out"], "out")
+    _close(torch.cat(dxs).cpu(), want["dx"], "dx")
+    _close(torch.cat(dws).reshape(-1, K).cpu(), want["dweights"], "dweights")
+    _close(torch.cat(dw_ups).cpu(), want["dw_up"], "dw_up")
+    _close(torch.cat(dw_downs).cpu(), want["dw_down"], "dw_down")
+    # a second pass through the same workspace: counters, credits and double buffers carry over
+    outs2, saved2 = world.forward(xs, idl, wl, ups, downs)
+    torch.cuda.synchronize()
+    assert all(torch.equal(a, b) for a, b in zip(outs, outs2)), "the forward must be bitwise reproducible"
+    world.close()
+
+
+def test_bounded_wait_reports_instead_of_hanging():
+    """A wait on a counter nobody advances runs out after its limit and leaves an error status; the context survives."""
+    from chunked_ep_moe_b200 import _build
+
+    ext = _build.load()
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(8, dtype=torch.int32, device="cuda")
+    ext.wait_probe(flag, 5, 2000, status)
+    torch.cuda.synchronize()
+    st = status.cpu().tolist()
+    assert st[0] == 2 and st[1] == 5 and st[5] == 5 and st[6] == 0, st
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0  # the device still answers

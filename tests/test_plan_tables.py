@@ -1,0 +1,89 @@
+"""The extension's per-pass plan tables (the code the single-CTA plan kernel runs) vs the torch planner."""
+
+import numpy as np
+import pytest
+import torch
+
+from chunked_ep_moe_b200 import _build
+from chunked_ep_moe_b200.ops import plan as plan_lib
+
+
+def _counts(P, L, tokens, top_k, skew, seed):
+    gen = torch.Generator().manual_seed(seed)
+    E = P * L
+    logits = torch.randn(P * tokens, E, generator=gen)
+    if skew == "all_one":
+        logits[:, 0] += 100.0
+    elif skew == "empty":  # some experts get nothing at all
+        logits[:, 1::3] -= 100.0
+    ids = torch.topk(logits, top_k, dim=1).indices.reshape(P, tokens, top_k)
+    sc = [plan_lib.sort_and_count(ids[r], E) for r in range(P)]
+    counts = torch.stack([c.reshape(P, L) for _, c in sc])
+    return ids, [o for o, _ in sc], counts
+
+
+@pytest.mark.parametrize("P,L,S", [(1, 4, 16), (2, 2, 4), (4, 2, 5), (8, 4, 24), (4, 8, 1000)])
+@pytest.mark.parametrize("skew", ["uniform", "all_one", "empty"])
+def test_tables_match_torch_planner(P, L, S, skew):
+    ext = _build.load()
+    tokens, top_k = 16, 2
+    ids, orders, counts = _counts(P, L, tokens, top_k, skew, seed=P * 100 + L)
+    max_slices = P * tokens * top_k // S + 2
+    lay = ext.plan_layout(P, L, S, max_slices)
+    n = P * L
+    for me in range(P):
+        ref = plan_lib.plan_from_counts(orders[me], counts, S, me)
+        tab = ext.plan_build_host(counts.to(torch.int32).contiguous(), S, max_slices, me).numpy()
+        assert tab[0] == ref.num_slices
+        assert tab[1] == int(plan_lib.stream_rows(ref)[me])
+        assert tab[5] == tokens * top_k
+        sl = lambda key, cnt: tab[lay[key]: lay[key] + cnt]
+        np.testing.assert_array_equal(sl("send_start", n), ref.send_start[me].numpy())
+        np.testing.assert_array_equal(sl("seg_start", n), ref.recv_start[:, :, me].reshape(-1).numpy())
+        np.testing.assert_array_equal(sl("seg_size", n), ref.counts[me].reshape(-1).numpy())
+        np.testing.assert_array_equal(sl("in_start", n), ref.recv_start[me].transpose(0, 1).reshape(-1).numpy())
+        np.testing.assert_array_equal(sl("in_size", n), ref.counts[:, me, :].reshape(-1).numpy())
+        np.testing.assert_array_equal(sl("src_send_start", n),
+                                      ref.send_start.reshape(P, P, L)[:, me, :].reshape(-1).numpy())
+        np.testing.assert_array_equal(sl("expert_start", L), ref.expert_start[me].numpy())
+        np.testing.assert_array_equal(sl("expert_rows", L), ref.expert_rows[me].numpy())
+        seen_final = np.zeros(L, dtype=np.int64)
+        for j in range(max_slices):
+            d = plan_lib.dispatch_args(ref, j, S)
+            groups = plan_lib.slice_group_sizes(ref, j, S).numpy()
+            put = tab[lay["put"] + 4 * n * j: lay["put"] + 4 * n * (j + 1)].reshape(n, 4)
+            if j < ref.num_slices:
+                np.testing.assert_array_equal(put[:, 1], d.send_sizes.numpy())
+                live = put[:, 1] > 0
+                np.testing.assert_array_equal(put[live, 0], d.input_offsets.numpy()[live])
+                np.testing.assert_array_equal(put[live, 2], d.output_offsets.numpy()[live])
+                chunks = -(-put[:, 1] // lay["put_chunk_rows"])
+                np.testing.assert_array_equal(put[:, 3], np.cumsum(chunks) - chunks)
+                assert tab[lay["num_chunks"] + j] == chunks.sum()
+            else:
+                assert tab[lay["num_chunks"] + j] == 0
+            # row tiles: cover each expert's rows of the slice exactly, in expert order, 128 rows at most
+            num_m = tab[lay["num_mtiles"] + j]
+            mt = tab[lay["mtiles"] + 4 * lay["max_mtiles"] * j:][: 4 * num_m].reshape(num_m, 4)
+            starts = np.cumsum(groups) - groups
+            covered = np.zeros(L, dtype=np.int64)
+            for e, row0, nrows, _ in mt:
+                assert 0 < nrows <= lay["tile_m"]
+                assert row0 == starts[e] + covered[e]
+                covered[e] += nrows
+            np.testing.assert_array_equal(covered, groups if j < ref.num_slices else 0 * groups)
+            # weight-gradient groups: one per expert present; first/final flags; empty experts once in slice 0
+            num_g = tab[lay["num_gtiles"] + j]
+            gt = tab[lay["gtiles"] + 4 * lay["max_gtiles"] * j:][: 4 * num_g].reshape(num_g, 4)
+            for e, row0, nrows, flags in gt:
+                es, er = int(ref.expert_start[me][e]), int(ref.expert_rows[me][e])
+                if nrows == 0:
+                    assert j == 0 and er == 0 and flags == 3
+                else:
+                    assert nrows == groups[e] and row0 == starts[e]
+                    assert bool(flags & 1) == (es >= j * S)
+                    assert bool(flags & 2) == (es + er <= (j + 1) * S)
+                seen_final[e] += bool(flags & 2)
+            present = set(gt[:, 0].tolist())
+            assert present >= {e for e in range(L) if groups[e] > 0}
+        np.testing.assert_array_equal(seen_final, np.ones(L))  # every expert's gradient is finalised exactly once
