@@ -188,8 +188,8 @@ __global__ void __launch_bounds__(256) combine_reduce_kernel(const CombineParams
   }
 }
 
-__global__ void __launch_bounds__(256) dequant_slice_kernel(const uint8_t* q, const float* scales,
-                                                            __nv_bfloat16* out, int rows, int hidden) {
+__device__ __forceinline__ void dequant_rows(const uint8_t* q, const float* scales, __nv_bfloat16* out, int rows,
+                                             int hidden) {
   const int units = hidden >> 3;  // 8 values per thread step
   const size_t total = static_cast<size_t>(rows) * units;
   for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total;
@@ -209,6 +209,28 @@ __global__ void __launch_bounds__(256) dequant_slice_kernel(const uint8_t* q, co
     *reinterpret_cast<int4*>(out + row * hidden + static_cast<size_t>(u) * 8) =
         make_int4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
   }
+}
+
+__global__ void __launch_bounds__(256) dequant_slice_kernel(const DequantParams p) {
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) s_abort = 0;
+  __syncthreads();
+  const int n = p.lay.P * p.lay.L;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int through = plan_clip((p.slice + 1) * p.lay.S - p.plan[p.lay.off_in_start + i], 0,
+                                  p.plan[p.lay.off_in_size + i]);
+    const uint32_t target = p.pass_base[i] + static_cast<uint32_t>(through);
+    uint32_t seen = 0;
+    if (!spin_until_reached(p.arrive + i, target, p.spin_limit, &seen)) {
+      report_status(p.status, kStatusArrivalTimeout, kKernelPut, 1, p.slice, i, target, seen);
+      s_abort = 1;
+    }
+  }
+  __syncthreads();
+  if (s_abort) return;
+  const int rows = plan_clip(p.plan[1] - p.slice * p.lay.S, 0, p.lay.S);
+  dequant_rows(p.xq, p.xs, p.x, rows, p.hidden);
+  if (p.gq != nullptr) dequant_rows(p.gq, p.gs, p.g, rows, p.hidden);
 }
 
 __global__ void wait_probe_kernel(const uint32_t* flag, uint32_t target, uint32_t spin_limit, StatusBlock* status) {
@@ -238,10 +260,8 @@ void launch_combine_reduce(const CombineParams& p, cudaStream_t stream) {
   combine_reduce_kernel<<<grid, 256, 0, stream>>>(p);
 }
 
-void launch_dequant_slice(const uint8_t* q, const float* scales, __nv_bfloat16* out, int rows, int hidden,
-                          cudaStream_t stream) {
-  if (rows <= 0) return;
-  dequant_slice_kernel<<<592, 256, 0, stream>>>(q, scales, out, rows, hidden);
+void launch_dequant_slice(const DequantParams& p, cudaStream_t stream) {
+  dequant_slice_kernel<<<592, 256, 0, stream>>>(p);
 }
 
 void launch_wait_probe(const uint32_t* flag, uint32_t target, uint32_t spin_limit, StatusBlock* status,

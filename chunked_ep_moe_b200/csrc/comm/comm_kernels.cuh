@@ -58,9 +58,27 @@ struct CombineParams {
 
 void launch_combine_reduce(const CombineParams& p, cudaStream_t stream);
 
-// Receiver-side dequantisation of an arrived fp8 slice into the bf16 slice buffer the GEMMs read.
-void launch_dequant_slice(const uint8_t* q, const float* scales, __nv_bfloat16* out, int rows, int hidden,
-                          cudaStream_t stream);
+// Receiver-side expansion of an arrived fp8 slice (e4m3 + one fp32 scale per 128 columns) into the bf16
+// slice buffer the GEMMs read. The kernel is the slice's first consumer, so it acquires the arrival
+// counters of every (source, expert) segment of the slice itself before it reads anything.
+struct DequantParams {
+  const int* plan;
+  PlanLayout lay;
+  int slice;
+  int hidden;
+  const uint32_t* arrive;
+  const uint32_t* pass_base;
+  const uint8_t* xq;          // [S, D] e4m3
+  const float* xs;            // [S, D/128]
+  __nv_bfloat16* x;           // [S, D]
+  const uint8_t* gq;          // backward: the output gradient's slice, or null
+  const float* gs;
+  __nv_bfloat16* g;
+  uint32_t spin_limit;
+  StatusBlock* status;
+};
+
+void launch_dequant_slice(const DequantParams& p, cudaStream_t stream);
 
 // Bounded-wait self test: waits on a counter nobody advances and reports through `status`.
 void launch_wait_probe(const uint32_t* flag, uint32_t target, uint32_t spin_limit, StatusBlock* status,

@@ -322,6 +322,30 @@ const CUtensorMap& FusedRank::weight_map(const torch::Tensor& w, uint32_t box_ro
   return it->second;
 }
 
+void FusedRank::dequant(const int* plan, int j, int b, bool with_g, cudaStream_t st) {
+  // Rows arrived as e4m3 + block scales: expand them into the bf16 slice buffers the GEMMs read.
+  DequantParams d{};
+  d.plan = plan;
+  d.lay = lay_;
+  d.slice = j;
+  d.hidden = D_;
+  d.arrive = reinterpret_cast<const uint32_t*>(arena_ + arena_lay_.arrive);
+  d.pass_base = reinterpret_cast<const uint32_t*>(pass_base_.data_ptr());
+  const size_t rows_off = static_cast<size_t>(b) * S_;
+  d.xq = arena_ + arena_lay_.xq + rows_off * D_;
+  d.xs = reinterpret_cast<const float*>(arena_ + arena_lay_.xs) + rows_off * (D_ / 128);
+  d.x = reinterpret_cast<__nv_bfloat16*>(arena_ + arena_lay_.xbuf) + rows_off * D_;
+  if (with_g) {
+    d.gq = arena_ + arena_lay_.gq + rows_off * D_;
+    d.gs = reinterpret_cast<const float*>(arena_ + arena_lay_.gs) + rows_off * (D_ / 128);
+    d.g = reinterpret_cast<__nv_bfloat16*>(arena_ + arena_lay_.gbuf) + rows_off * D_;
+  }
+  d.spin_limit = spin_limit_;
+  d.status = reinterpret_cast<StatusBlock*>(status_.data_ptr());
+  launch_dequant_slice(d, st);
+  ++launches_;
+}
+
 void FusedRank::launch_gemm(int mode, const GemmParams& p, const CUtensorMap& a, const CUtensorMap& b,
                             cudaStream_t st) {
   launch_grouped_gemm(mode, p, a, b, num_sms_, st);
@@ -347,16 +371,13 @@ void FusedRank::compute_forward(int64_t j, torch::Tensor plan, torch::Tensor w_u
   const uint32_t seq = seq_ + static_cast<uint32_t>(j);
   const int b = static_cast<int>(seq & 1u);
   const int* pl = plan.data_ptr<int>();
-  if (fp8_) {
-    // Rows arrived as e4m3 + block scales: expand them into the bf16 slice buffer the GEMM reads.
-    // (The put of this slice has completed on this rank's stream; remote rows are acquired by the GEMM below.)
-  }
+  if (fp8_) dequant(pl, static_cast<int>(j), b, /*with_g=*/false, st);
   {
     GemmParams p = base_params(pl, static_cast<int>(j));
     p.n_tiles = 2 * F_ / kBlockN;
     p.k_blocks = D_ / kBlockK;
     p.b_group_rows = D_;
-    p.arrive = reinterpret_cast<const uint32_t*>(arena_ + arena_lay_.arrive);
+    p.arrive = fp8_ ? nullptr : reinterpret_cast<const uint32_t*>(arena_ + arena_lay_.arrive);
     p.pass_base = reinterpret_cast<const uint32_t*>(pass_base_.data_ptr());
     p.out0 = reinterpret_cast<__nv_bfloat16*>(act_.data_ptr());
     p.ld0 = F_;
@@ -392,12 +413,13 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
   const int* pl = plan.data_ptr<int>();
   const int par = static_cast<int>(j & 1);
   const int dwp_tiles = D_ / kBlockN;
+  if (fp8_) dequant(pl, static_cast<int>(j), b, /*with_g=*/true, st);
   {  // remat: act and h
     GemmParams p = base_params(pl, static_cast<int>(j));
     p.n_tiles = 2 * F_ / kBlockN;
     p.k_blocks = D_ / kBlockK;
     p.b_group_rows = D_;
-    p.arrive = reinterpret_cast<const uint32_t*>(arena_ + arena_lay_.arrive);
+    p.arrive = fp8_ ? nullptr : reinterpret_cast<const uint32_t*>(arena_ + arena_lay_.arrive);
     p.pass_base = reinterpret_cast<const uint32_t*>(pass_base_.data_ptr());
     p.out0 = reinterpret_cast<__nv_bfloat16*>(act_.data_ptr());
     p.ld0 = F_;

@@ -73,6 +73,7 @@ class FusedRank {
   void end_pass(int64_t n_slices);
   GemmParams base_params(const int* plan, int j) const;
   const CUtensorMap& weight_map(const torch::Tensor& w, uint32_t box_rows);
+  void dequant(const int* plan, int j, int b, bool with_g, cudaStream_t st);
   void launch_gemm(int mode, const GemmParams& p, const CUtensorMap& a, const CUtensorMap& b, cudaStream_t st);
 
   int P_, L_, me_, S_, D_, F_, K_, stripe_, tk_cap_, max_slices_, num_sms_, put_blocks_;

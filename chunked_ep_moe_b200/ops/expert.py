@@ -63,7 +63,7 @@ def gmm(lhs: torch.Tensor, rhs: torch.Tensor, group_sizes: torch.Tensor, out_dty
 
 
 def tgmm(lhs: torch.Tensor, rhs: torch.Tensor, group_sizes: torch.Tensor) -> torch.Tensor:
-    """Per-group `lhs[rows_g]^T @ rhs[rows_g]` -> `[G, lhs_cols, rhs_cols]` float32.
+    """Per-group `lhs[rows_g]^T @ rhs[rows_g]` -> `[G, lhs_cols, rhs_cols]` (fp32 accumulate; fp32 out off the library path).
 
     Only rows inside a group are read, so NaN-poisoned padding rows cannot leak
     into a weight gradient (the reference masks with select for the same
@@ -73,7 +73,7 @@ def tgmm(lhs: torch.Tensor, rhs: torch.Tensor, group_sizes: torch.Tensor) -> tor
     if _use_library_grouped_mm(lhs):
         # Ragged contraction dim: [cols_l, rows] x [rows, cols_r] with offsets over rows -> [G, cols_l, cols_r].
         offs = torch.cumsum(group_sizes.to(torch.int32), 0, dtype=torch.int32)
-        return F.grouped_mm(lhs.t(), rhs, offs=offs).float()
+        return F.grouped_mm(lhs.t(), rhs, offs=offs)  # library output dtype; the caller accumulates in fp32
     out = lhs.new_zeros((num_groups, lhs.shape[1], rhs.shape[1]), dtype=torch.float32)
     for g, (a, b) in enumerate(_group_bounds(group_sizes)):
         if b > a:

@@ -130,8 +130,8 @@ def backward_loop(x: torch.Tensor, weights: torch.Tensor, w_up: torch.Tensor, w_
         back = plan_lib.combine_args(plan, j, s)
         dx_rows = exchange(grads.dx, dx_rows, back, group)
         dw_rows = exchange(d_weight, dw_rows, back, group)
-        dw_up += grads.dw_up.to(accum)
-        dw_down += grads.dw_down.to(accum)
+        dw_up.add_(grads.dw_up)  # accumulates in `accum` whatever dtype the grouped GEMM returned
+        dw_down.add_(grads.dw_down)
         cur = nxt
 
     dx = torch.zeros((num_tokens, hidden), dtype=torch.float32, device=x.device)

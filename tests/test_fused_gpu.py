@@ -172,6 +172,38 @@ def test_lockstep_multi_rank_matches_oracle(world_size, skew, slice_size):
     world.close()
 
 
+@pytest.mark.parametrize("world_size,skew", [(1, "uniform"), (4, "uniform"), (4, "all_one")])
+def test_fp8_wire_is_close(world_size, skew):
+    """Rows travel as e4m3 with one fp32 scale per 1x128 block; outputs stay within e4m3 error of the oracle."""
+    from chunked_ep_moe_b200.parallel.lockstep import LockstepWorld
+
+    T, E, K, D, F, stripe, S = 64, 8, 2, 256, 256, 64, 128
+    x, ids, weights, w_up, w_down, g = moe_cases.setup(world_size, T, E, K, D, F, skew, seed=5)
+    cfg = ChunkedMoEConfig(num_experts=E, top_k=K, slice_size=S, transport="nvshmem", expert_compute="fused",
+                           stripe_width=stripe, comm_dtype="float8_e4m3fn")
+    bf = lambda t: t.cuda().to(torch.bfloat16).contiguous()
+    sh = lambda t, r: moe_cases.shard(t, r, world_size)
+    xs = [bf(sh(x, r)) for r in range(world_size)]
+    gs = [bf(sh(g, r)) for r in range(world_size)]
+    idl = [sh(ids, r).cuda() for r in range(world_size)]
+    wl = [sh(weights, r).cuda() for r in range(world_size)]
+    ups = [bf(sh(w_up, r)) for r in range(world_size)]
+    downs = [bf(sh(w_down, r)) for r in range(world_size)]
+    world = LockstepWorld(cfg, world_size, D, F, T)
+    outs, saved = world.forward(xs, idl, wl, ups, downs)
+    dxs, dws, dw_ups, dw_downs = world.backward(xs, gs, ups, downs, saved)
+    torch.cuda.synchronize()
+    want = _oracle_dev(torch.cat(xs), ids, weights, torch.cat(ups), torch.cat(downs), torch.cat(gs), stripe)
+    got = {"out": torch.cat(outs), "dx": torch.cat(dxs), "dweights": torch.cat(dws).reshape(-1, K),
+           "dw_up": torch.cat(dw_ups), "dw_down": torch.cat(dw_downs)}
+    for name, val in got.items():
+        a, b = val.float().cpu(), want[name].float()
+        assert torch.isfinite(a).all(), name
+        rel = float((a - b).norm() / b.norm())
+        assert rel < 0.08, f"{name}: relative error {rel:.4f}"
+    world.close()
+
+
 def test_bounded_wait_reports_instead_of_hanging():
     """A wait on a counter nobody advances runs out after its limit and leaves an error status; the context survives."""
     from chunked_ep_moe_b200 import _build

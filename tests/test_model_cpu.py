@@ -1,0 +1,99 @@
+"""The decoder, router, checkpoint helpers and stats on CPU (fp32, collective transport)."""
+
+import torch
+
+from chunked_ep_moe_b200.models.deepseek_tiny import DeepSeekTiny, DeepSeekTinyConfig
+from chunked_ep_moe_b200.ops.striping import stripe_weights, unstripe_weights
+from chunked_ep_moe_b200.utils import checkpoint as ckpt
+from chunked_ep_moe_b200.utils import stats
+
+
+def _tiny_cfg(**kw):
+    base = dict(vocab_size=97, d_model=32, n_layers=3, n_heads=2, head_dim=16, dense_ffn=64, num_experts=4, moe_ffn=16,
+                top_k=2, shared_ffn=16, slice_size=16, stripe_width=4, transport="emulated",
+                expert_compute="reference")
+    base.update(kw)
+    return DeepSeekTinyConfig(**base)
+
+
+def test_decoder_trains_on_cpu():
+    torch.manual_seed(0)
+    cfg = _tiny_cfg()
+    model = DeepSeekTiny(cfg)
+    model.init_weights(seed=1)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-2)
+    tokens = torch.randint(0, cfg.vocab_size, (2, 17))
+    losses = []
+    for _ in range(8):
+        opt.zero_grad()
+        ce, aux = model(tokens[:, :-1], tokens[:, 1:])
+        (ce + aux).backward()
+        opt.step()
+        for r in model.routers():
+            r.update_bias()
+        losses.append(float(ce.detach()))
+    assert all(p.grad is not None for p in model.parameters())
+    assert losses[-1] < losses[0], losses
+    assert float(aux) > 0
+
+
+def test_slice_size_does_not_change_the_model():
+    """Chunking is an execution detail: S=4 and S=1000 give the same loss and gradients."""
+    tokens = torch.randint(0, 97, (2, 13), generator=torch.Generator().manual_seed(3))
+    outs = []
+    for s in (4, 1000):
+        model = DeepSeekTiny(_tiny_cfg(slice_size=s))
+        model.init_weights(seed=5)
+        ce, aux = model(tokens[:, :-1], tokens[:, 1:])
+        (ce + aux).backward()
+        outs.append((ce.detach(), model.blocks[1].ffn.w_up.grad.clone(), model.embed.weight.grad.clone()))
+    assert torch.allclose(outs[0][0], outs[1][0], atol=1e-6)
+    assert torch.allclose(outs[0][1], outs[1][1], atol=1e-6)
+    assert torch.allclose(outs[0][2], outs[1][2], atol=1e-6)
+
+
+def test_checkpoint_roundtrip_and_unstriped_export(tmp_path):
+    cfg = _tiny_cfg()
+    model = DeepSeekTiny(cfg)
+    model.init_weights(seed=2)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+    tokens = torch.randint(0, cfg.vocab_size, (1, 9))
+    ce, aux = model(tokens[:, :-1], tokens[:, 1:])
+    (ce + aux).backward()
+    opt.step()
+    ckpt.save_checkpoint(str(tmp_path), model, opt, step=7, rank=0)
+
+    other = DeepSeekTiny(cfg)
+    other.init_weights(seed=99)
+    opt2 = torch.optim.AdamW(other.parameters(), lr=1e-3)
+    assert ckpt.load_checkpoint(str(tmp_path), other, opt2, rank=0) == 7
+    for (n1, p1), (_, p2) in zip(model.state_dict().items(), other.state_dict().items()):
+        assert torch.equal(p1, p2), n1
+
+    exported = ckpt.export_unstriped(model.state_dict(), cfg.stripe_width)
+    assert any(k.endswith("w_gate") for k in exported) and not any(k.endswith(".w_up") for k in exported)
+    back = ckpt.import_unstriped(exported, cfg.stripe_width)
+    for k, v in model.state_dict().items():
+        assert torch.equal(back[k], v), k
+
+
+def test_stripe_roundtrip():
+    gate, up = torch.randn(3, 8, 12), torch.randn(3, 8, 12)
+    for stripe in (1, 4, 12):
+        w = stripe_weights(gate, up, stripe)
+        assert w.shape == (3, 8, 24)
+        g2, u2 = unstripe_weights(w, stripe)
+        assert torch.equal(g2, gate) and torch.equal(u2, up)
+        assert torch.equal(w[..., :stripe], gate[..., :stripe]) and torch.equal(w[..., stripe:2 * stripe], up[..., :stripe])
+
+
+def test_stats_helpers():
+    wb = stats.wire_bytes(1000, 7168, None, backward=False)
+    assert wb["dispatch_bytes"] == 1000 * (7168 * 2 + 4) and wb["combine_bytes"] == 1000 * 7168 * 2
+    wq = stats.wire_bytes(1000, 7168, "float8_e4m3fn", backward=True)
+    assert wq["dispatch_bytes"] == 1000 * (2 * (7168 + 56 * 4) + 4)
+    assert stats.layer_flops(10, 4, 2, False) == 10 * 4 * 2 * 6
+    rl = stats.roofline_ms(23.09e12, 4.11e9, {"bf16_tflops_sustained": 1368.3, "bf16_tflops": 1629.7})
+    assert abs(rl["compute_ms"] - 16.87) < 0.05 and rl["roofline_ms"] == rl["compute_ms"]
+    hs = stats.header_stats([3, 20, 24, 5, 0, 16] + [0] * 10, 8)
+    assert hs["my_active_slices"] == 3 and hs["my_padding_rows"] == 4
