@@ -83,6 +83,35 @@ __device__ __forceinline__ void resolve_source(const GemmParams& p, int g, int g
   }
 }
 
+// Issues the TMA loads of one k-block of a tile into a pipeline stage (completing on `bar`).
+// (An L2 prefetch cursor running 8 k-blocks ahead of these loads was measured and made the GEMM
+// modes ~14% slower at DeepSeek-V3 sizes, so there is none.)
+template <int MODE>
+__device__ __forceinline__ void issue_kblock(const GemmParams& p, const Tile& tl, int kb, const CUtensorMap* map_a,
+                                             const CUtensorMap* map_b, uint32_t sa, uint32_t sb, uint32_t bar) {
+  using Traits = ModeTraits<MODE>;
+  auto go = [&](const CUtensorMap* map, uint32_t dst, int x, int y) { tma_load_2d(dst, map, bar, x, y); };
+  if constexpr (Traits::kAMn) {
+    // lhs [S, M]: k runs over rows; two 64-column chunks of the 128-wide row tile.
+    go(map_a, sa, tl.m * kBlockM, tl.row0 + kb * kBlockK);
+    go(map_a, sa + 8192, tl.m * kBlockM + 64, tl.row0 + kb * kBlockK);
+  } else {
+    go(map_a, sa, kb * kBlockK, tl.row0);
+  }
+  if constexpr (MODE == kModeTgmm) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) go(map_b, sb + c * 8192, tl.n * kBlockN + c * 64, tl.row0 + kb * kBlockK);
+  } else if constexpr (Traits::kBMn) {
+    // weights [L*K, N]: four 64-column chunks of the 256-wide column tile.
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+      go(map_b, sb + c * 8192, tl.n * kBlockN + c * 64, tl.g * p.b_group_rows + kb * kBlockK);
+  } else {
+    // weights [L*N, K] read as K-major B: 256 rows x 64 k.
+    go(map_b, sb, kb * kBlockK, tl.g * p.b_group_rows + tl.n * kBlockN);
+  }
+}
+
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
 
 template <int MODE>
@@ -178,27 +207,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
           const uint32_t sa = smem_base + s * kStageBytes;
           const uint32_t sb = sa + kStageBytesA;
           mbar_expect_tx(full_bar(s), kStageBytes);
-          if constexpr (Traits::kAMn) {
-            // lhs [S, M]: k runs over rows; two 64-column chunks of the 128-wide row tile.
-            tma_load_2d(sa, &map_a, full_bar(s), tl.m * kBlockM, tl.row0 + kb * kBlockK);
-            tma_load_2d(sa + 8192, &map_a, full_bar(s), tl.m * kBlockM + 64, tl.row0 + kb * kBlockK);
-          } else {
-            tma_load_2d(sa, &map_a, full_bar(s), kb * kBlockK, tl.row0);
-          }
-          if constexpr (MODE == kModeTgmm) {
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-              tma_load_2d(sb + c * 8192, &map_b, full_bar(s), tl.n * kBlockN + c * 64, tl.row0 + kb * kBlockK);
-          } else if constexpr (Traits::kBMn) {
-            // weights [L*K, N]: four 64-column chunks of the 256-wide column tile.
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-              tma_load_2d(sb + c * 8192, &map_b, full_bar(s), tl.n * kBlockN + c * 64,
-                          tl.g * p.b_group_rows + kb * kBlockK);
-          } else {
-            // weights [L*N, K] read as K-major B: 256 rows x 64 k.
-            tma_load_2d(sb, &map_b, full_bar(s), kb * kBlockK, tl.g * p.b_group_rows + tl.n * kBlockN);
-          }
+          issue_kblock<MODE>(p, tl, kb, &map_a, &map_b, sa, sb, full_bar(s));
         }
       }
       __syncwarp();
@@ -490,11 +499,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
         const bool first = (tl.flags & kGroupFirst) != 0, final = (tl.flags & kGroupFinal) != 0;
         const float* cin = p.carry_in + row_off;
         float* cout = p.carry_out + row_off;
-        __nv_bfloat16* gout = p.grad_out + static_cast<size_t>(tl.g) * m_total * n_total + row_off;
-#pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
+        auto load_chunk = [&](int col) {
           if (tl.kblocks > 0) {
-            tmem_ld_32x32(tacc + c * 32, r);
+            tmem_ld_32x32(tacc + col, r);
             tmem_ld_wait();
           } else {
 #pragma unroll
@@ -503,22 +510,47 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
           if (!first) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              const float4 pv = *reinterpret_cast<const float4*>(cin + c * 32 + 4 * i);
+              const float4 pv = *reinterpret_cast<const float4*>(cin + col + 4 * i);
               r[4 * i] = __float_as_uint(__uint_as_float(r[4 * i]) + pv.x);
               r[4 * i + 1] = __float_as_uint(__uint_as_float(r[4 * i + 1]) + pv.y);
               r[4 * i + 2] = __float_as_uint(__uint_as_float(r[4 * i + 2]) + pv.z);
               r[4 * i + 3] = __float_as_uint(__uint_as_float(r[4 * i + 3]) + pv.w);
             }
           }
-          if (final) {
+        };
+        if (final) {
+          // bf16 gradient: transpose through the warp's staging buffer so every store instruction
+          // writes two full 256-byte row pieces instead of 32 scattered 16-byte ones.
+          __nv_bfloat16* warp_out = p.grad_out + static_cast<size_t>(tl.g) * m_total * n_total +
+                                    static_cast<size_t>(tl.m * kBlockM + q * 32) * n_total + tl.n * kBlockN;
+#pragma unroll 1
+          for (int half = 0; half < 2; ++half) {
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              load_chunk(half * 128 + c * 32);
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              *reinterpret_cast<int4*>(gout + c * 32 + 8 * i) =
-                  make_int4(pack_bf16(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])),
-                            pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
-                            pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])),
-                            pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7])));
-          } else {
+              for (int i = 0; i < 4; ++i) {
+                const int lc = c * 4 + i;
+                *reinterpret_cast<int4*>(stage_gen + lane * 256 + ((lc ^ (lane & 15)) << 4)) =
+                    make_int4(pack_bf16(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])),
+                              pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
+                              pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])),
+                              pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7])));
+              }
+            }
+            __syncwarp();
+#pragma unroll 4
+            for (int rr = 0; rr < 16; ++rr) {
+              const int rsel = rr * 2 + (lane >> 4), c16 = lane & 15;
+              const int4 v = *reinterpret_cast<const int4*>(stage_gen + rsel * 256 + ((c16 ^ (rsel & 15)) << 4));
+              *reinterpret_cast<int4*>(warp_out + static_cast<size_t>(rsel) * n_total + half * 128 + c16 * 8) = v;
+            }
+            __syncwarp();
+          }
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < 8; ++c) {
+            load_chunk(c * 32);
 #pragma unroll
             for (int i = 0; i < 8; ++i)
               *reinterpret_cast<float4*>(cout + c * 32 + 4 * i) =
