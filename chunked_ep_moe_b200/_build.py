@@ -24,6 +24,7 @@ _SOURCES = [
     "gemm/grouped_gemm.cu",
     "comm/comm_kernels.cu",
     "plan/plan_kernel.cu",
+    "plan/expert_sort_noalloc.cu",
 ]
 _lock = threading.Lock()
 _module = None
