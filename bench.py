@@ -236,10 +236,41 @@ def main():
         e2e_ms = e0.elapsed_time(e1) / args.steps
     clocks = sampler.stop()
 
-    t = torch.tensor([ms, e2e_ms if not args.no_e2e else 0.0], device=dev, dtype=torch.float64)
+    # Exposed all-to-all: the same per-GPU work (same L experts, same rows per expert in expectation) with every
+    # row local, i.e. this rank alone as a 1-rank expert-parallel group, timed the same way.
+    local_ms = None
+    if world > 1 and fused:
+        solo = None
+        for r in range(world):  # every rank must take part in creating every subgroup
+            g_r = dist.new_group([r])
+            if r == rank:
+                solo = g_r
+        cfg_local = ChunkedMoEConfig(num_experts=L, top_k=K, slice_size=S, stripe_width=c["stripe"],
+                                     transport="nvshmem", expert_compute="fused", comm_dtype=args.comm_dtype)
+        ids_l, weights_l = make_routing(gen, T, L, K, "none", dev)
+
+        def step_local():
+            x = x_d.detach().requires_grad_(True)
+            w = weights_l.detach().requires_grad_(True)
+            w_up.grad = None
+            w_down.grad = None
+            chunked_moe(x, ids_l, w, w_up, w_down, cfg_local, solo).backward(g_d)
+
+        for _ in range(3):
+            step_local()
+        sync_all()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(args.steps):
+            step_local()
+        s1.record()
+        sync_all()
+        local_ms = s0.elapsed_time(s1) / args.steps
+
+    t = torch.tensor([ms, e2e_ms if not args.no_e2e else 0.0, local_ms or 0.0], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
-    ms, e2e_ms = float(t[0]), float(t[1])
+    ms, e2e_ms, local_ms = float(t[0]), float(t[1]), (float(t[2]) if local_ms is not None else None)
     if not args.no_e2e:
         h2d = x_h.numel() * 2 + ids_h.numel() * 4 + weights_h.numel() * 4
         e2e = {"value": world * T / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
@@ -280,6 +311,8 @@ def main():
             "clocks": clocks,
             "e2e": e2e,
             "gpu_launches": int(n_launch),
+            "local_only_ms_per_step": local_ms,
+            "exposed_a2a_ms_per_step": (ms - local_ms) if local_ms is not None else (0.0 if world == 1 else None),
         }
         print(json.dumps(result))
     if world > 1:

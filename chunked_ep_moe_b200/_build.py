@@ -22,6 +22,7 @@ _SOURCES = [
     "runtime/tensor_map.cpp",
     "runtime/fused_rank.cpp",
     "gemm/grouped_gemm.cu",
+    "gemm/grouped_gemm_pair.cu",
     "comm/comm_kernels.cu",
     "plan/plan_kernel.cu",
     "plan/expert_sort_noalloc.cu",

@@ -3,6 +3,7 @@
 
 #include <ATen/cuda/CUDAContext.h>
 
+#include "gemm/grouped_gemm.cuh"
 #include "plan/plan_kernel.cuh"
 #include "runtime/fused_rank.h"
 
@@ -13,6 +14,9 @@ py::dict plan_layout_dict(int P, int L, int S, int max_slices) {
   py::dict d;
   d["max_mtiles"] = y.max_mtiles;
   d["max_gtiles"] = y.max_gtiles;
+  d["max_ptiles"] = y.max_ptiles;
+  d["num_ptiles"] = y.off_num_ptiles;
+  d["ptiles"] = y.off_ptiles;
   d["send_start"] = y.off_send_start;
   d["seg_start"] = y.off_seg_start;
   d["seg_size"] = y.off_seg_size;
@@ -82,14 +86,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("arena_zero", &cem::arena_zero);
   m.def("arena_fill", &cem::arena_fill, "cudaMemset of a byte range (tests poison data buffers with NaN patterns)");
   m.def("arena_layout", &arena_layout_dict, "byte offsets inside one rank's symmetric arena");
+  m.def("pair_grid_used", []() { return cem::g_pair_grid_used; }, "grid of the last CTA-pair GEMM launch");
   m.def("wait_probe", &wait_probe, "bounded-wait self test kernel");
   py::class_<cem::FusedRank>(m, "FusedRank")
       .def(py::init<int, int, int, int, int, int, int, int, int, int, int, bool, int64_t, std::vector<int64_t>, bool,
-                    int64_t, int>(),
+                    int64_t, int, bool>(),
            py::arg("P"), py::arg("L"), py::arg("me"), py::arg("S"), py::arg("D"), py::arg("F"), py::arg("K"),
            py::arg("stripe"), py::arg("tk_cap"), py::arg("max_slices"), py::arg("num_sms"), py::arg("fp8"),
            py::arg("arena"), py::arg("peer_arenas"), py::arg("use_comm_stream"), py::arg("spin_limit"),
-           py::arg("put_blocks"))
+           py::arg("put_blocks"), py::arg("cta_pairs") = true)
       .def("begin_forward", &cem::FusedRank::begin_forward)
       .def("sort_only", &cem::FusedRank::sort_only)
       .def("begin_backward", &cem::FusedRank::begin_backward)

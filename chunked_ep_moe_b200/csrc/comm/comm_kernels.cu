@@ -92,8 +92,9 @@ __global__ void __launch_bounds__(kPutThreads) dispatch_put_kernel(const PutPara
   __shared__ int s_abort;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_seg = p.lay.P * p.lay.L;
-  if (threadIdx.x == 0) s_abort = 0;
+  if (threadIdx.x == 0) s_abort = (p.status != nullptr && p.status->code != 0) ? 1 : 0;
   __syncthreads();
+  if (s_abort) return;  // an earlier kernel of this pass already gave up
   // Buffer reuse: sequence q overwrites what sequence q-2 used on every receiver.
   if (p.seq >= 2 && threadIdx.x < p.lay.P) {
     uint32_t seen = 0;
@@ -154,9 +155,9 @@ __global__ void pass_begin_kernel(const int* plan, PlanLayout lay, uint32_t* exp
 __global__ void __launch_bounds__(256) combine_reduce_kernel(const CombineParams p) {
   __shared__ int s_abort;
   if (threadIdx.x == 0) {
-    s_abort = 0;
+    s_abort = (p.status != nullptr && p.status->code != 0) ? 1 : 0;
     uint32_t seen = 0;
-    if (!spin_until_reached(p.count, p.target, p.spin_limit, &seen)) {
+    if (!s_abort && !spin_until_reached(p.count, p.target, p.spin_limit, &seen)) {
       report_status(p.status, kStatusReturnTimeout, kKernelCombineReduce, 0, 0, 0, p.target, seen);
       s_abort = 1;
     }
@@ -213,8 +214,9 @@ __device__ __forceinline__ void dequant_rows(const uint8_t* q, const float* scal
 
 __global__ void __launch_bounds__(256) dequant_slice_kernel(const DequantParams p) {
   __shared__ int s_abort;
-  if (threadIdx.x == 0) s_abort = 0;
+  if (threadIdx.x == 0) s_abort = (p.status != nullptr && p.status->code != 0) ? 1 : 0;
   __syncthreads();
+  if (s_abort) return;
   const int n = p.lay.P * p.lay.L;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const int through = plan_clip((p.slice + 1) * p.lay.S - p.plan[p.lay.off_in_start + i], 0,

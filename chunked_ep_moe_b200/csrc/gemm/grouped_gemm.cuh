@@ -40,8 +40,8 @@ struct GemmParams {
   int b_group_rows;  // rows one expert occupies in the flattened 2-D weight tensor map
   int me;            // this rank
   int stripe;        // SwiGLU stripe width (swiglu / dswiglu)
-  uint32_t spin_limit;
-  uint32_t mbar_limit;
+  uint32_t spin_limit;   // polls of a cross-GPU flag before giving up
+  uint32_t mbar_limit;   // microseconds a pipeline barrier may take before giving up
   StatusBlock* status;
   // --- arrival flags (swiglu consumer) -----------------------------------------------------
   const uint32_t* arrive;     // [P*L] cumulative rows received per (source, local expert); null = no wait
@@ -73,5 +73,12 @@ constexpr int kGemmSmemBytes = 1024 /*alignment slack*/ + kStages * kStageBytes 
 
 void launch_grouped_gemm(int mode, const GemmParams& p, const CUtensorMap& map_a, const CUtensorMap& map_b, int grid,
                          cudaStream_t stream);
+
+// CTA-pair variant (clusters of two CTAs, one 256 x 256 MMA per pair). Same parameters; K-major weight
+// maps must use 128-row boxes (each CTA loads its own half of the column tile). `grid` is rounded down
+// to an even number.
+extern int g_pair_grid_used;  // grid of the last CTA-pair launch (clamped to what is resident at once)
+void launch_grouped_gemm_pair(int mode, const GemmParams& p, const CUtensorMap& map_a, const CUtensorMap& map_b,
+                              int grid, cudaStream_t stream);
 
 }  // namespace cem

@@ -1,0 +1,409 @@
+// CTA-pair variant of the grouped GEMM engine: two CTAs of one cluster drive ONE 256 x 256 x 16
+// tcgen05.mma (cta_group::2). Each CTA stages only its own 128 rows of A and its own 128 columns
+// of B (32 KB per k-block instead of 48 KB), which is what lifts the single-CTA kernel's shared-memory
+// bandwidth bound and allows a 6-stage ring in the same 192 KB.
+//
+//   both CTAs   warp 0      TMA producer for the CTA's own A rows / B half, completing on the CTA's own
+//                           full barrier (plain CTA-local loads).
+//   leader      warp 1      waits for its own stage AND the peer's "stage ready" arrival, issues the pair
+//                           MMAs, commits to both CTAs' empty barriers and both accumulator-full barriers.
+//   peer        warp 1      relay: waits for its own stage, (weight-gradient mode) zero-fills rows past the
+//                           group, then arrives on the leader's peer-ready barrier.
+//   both CTAs   warps 2-5   epilogue of the CTA's own 128 x 256 accumulator half (same code as the
+//                           single-CTA kernel), then arrive on the leader's accumulator-empty barrier.
+//
+// A pair covers two consecutive 128-row tiles of ONE expert (they share its weights); an odd last tile is
+// a pair whose second half stores nothing. In the weight-gradient mode the pair splits the dense feature
+// dimension instead. Every wait is bounded; a CTA that gives up records a status and unwinds, and its
+// partner then runs into its own limits.
+#include "gemm_common.cuh"
+
+namespace cem {
+
+namespace {
+
+constexpr int kPairStages = 6;
+constexpr int kPairStageBytesA = kBlockM * kBlockK * 2;        // 16 KB: this CTA's 128 rows
+constexpr int kPairStageBytesB = (kBlockN / 2) * kBlockK * 2;  // 16 KB: this CTA's 128 columns
+constexpr int kPairStageBytes = kPairStageBytesA + kPairStageBytesB;
+constexpr int kPairBand = kRasterBand / 2;                     // pairs swept together across N
+
+// Tile as seen by CTA `rank` of the pair.
+template <int MODE>
+__device__ __forceinline__ Tile decode_pair_tile(const GemmParams& p, int t, int num_entries, int rank) {
+  Tile tl;
+  if constexpr (MODE == kModeTgmm) {
+    const int m_pairs = p.m_tiles / 2;
+    const int per_group = m_pairs * p.n_tiles;
+    const int gi = t / per_group, rem = t - gi * per_group;
+    const int4 e = reinterpret_cast<const int4*>(p.plan + p.lay.off_gtiles + 4 * p.lay.max_gtiles * p.slice)[gi];
+    tl.g = e.x; tl.row0 = e.y; tl.nrows = e.z; tl.flags = e.w;
+    const int mp = rem / p.n_tiles;
+    tl.m = 2 * mp + rank; tl.n = rem - mp * p.n_tiles;
+    tl.kblocks = (e.z + kBlockK - 1) / kBlockK;
+  } else {
+    const int band_tiles = kPairBand * p.n_tiles;
+    const int band = t / band_tiles, rem = t - band * band_tiles;
+    int width = num_entries - band * kPairBand;
+    width = width > kPairBand ? kPairBand : width;
+    tl.n = rem / width;
+    const int pi = band * kPairBand + (rem - tl.n * width);
+    const int4 e = reinterpret_cast<const int4*>(p.plan + p.lay.off_ptiles + 4 * p.lay.max_ptiles * p.slice)[pi];
+    tl.g = e.x;
+    tl.row0 = e.y + rank * kBlockM;
+    tl.nrows = plan_clip(e.z - rank * kBlockM, 0, kBlockM);
+    tl.flags = 0; tl.m = pi;
+    tl.kblocks = p.k_blocks;
+  }
+  return tl;
+}
+
+// `bar` is this CTA's own full barrier in the relay scheme (weight-gradient mode) and the LEADER's full barrier
+// otherwise (pair-aware loads credit the leader directly).
+template <int MODE>
+__device__ __forceinline__ void issue_pair_kblock(const GemmParams& p, const Tile& tl, int kb, int rank,
+                                                  const CUtensorMap* map_a, const CUtensorMap* map_b, uint32_t sa,
+                                                  uint32_t sb, uint32_t bar) {
+  using Traits = ModeTraits<MODE>;
+  auto tma_load_2d = [&](uint32_t dst, const CUtensorMap* map, uint32_t b, int x, int y) {
+    if constexpr (MODE == kModeTgmm) cem::tma_load_2d(dst, map, b, x, y); else tma_load_2d_pair(dst, map, b, x, y);
+  };
+  if constexpr (Traits::kAMn) {
+    tma_load_2d(sa, map_a, bar, tl.m * kBlockM, tl.row0 + kb * kBlockK);
+    tma_load_2d(sa + 8192, map_a, bar, tl.m * kBlockM + 64, tl.row0 + kb * kBlockK);
+  } else {
+    tma_load_2d(sa, map_a, bar, kb * kBlockK, tl.row0);
+  }
+  const int col0 = tl.n * kBlockN + rank * (kBlockN / 2);  // this CTA's half of the 256-wide column tile
+  if constexpr (MODE == kModeTgmm) {
+    tma_load_2d(sb, map_b, bar, col0, tl.row0 + kb * kBlockK);
+    tma_load_2d(sb + 8192, map_b, bar, col0 + 64, tl.row0 + kb * kBlockK);
+  } else if constexpr (Traits::kBMn) {
+    tma_load_2d(sb, map_b, bar, col0, tl.g * p.b_group_rows + kb * kBlockK);
+    tma_load_2d(sb + 8192, map_b, bar, col0 + 64, tl.g * p.b_group_rows + kb * kBlockK);
+  } else {
+    tma_load_2d(sb, map_b, bar, kb * kBlockK, tl.g * p.b_group_rows + col0);  // 128-row box
+  }
+}
+
+template <int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap map_a,
+                         const __grid_constant__ CUtensorMap map_b) {
+  using Traits = ModeTraits<MODE>;
+  // Weight-gradient k-blocks may need rows zeroed by the CTA that owns them, so that mode keeps a CTA-local full
+  // barrier and relays "my half is ready" to the leader; every other mode lets the TMA credit the leader directly.
+  constexpr bool kRelay = (MODE == kModeTgmm);
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t staging_base = smem_base + kPairStages * kPairStageBytes;
+  uint8_t* staging_gen = smem_gen + kPairStages * kPairStageBytes;
+  const uint32_t bar_base = staging_base + kStagingBytes;
+  // barriers: full[6], empty[6], peer_ready[6], acc_full[2], acc_empty[2], drain; then tmem slot, abort flag
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kPairStages + s); };
+  auto ready_bar = [&](int s) { return bar_base + 8u * (2 * kPairStages + s); };
+  auto acc_full_bar = [&](int s) { return bar_base + 8u * (3 * kPairStages + s); };
+  auto acc_empty_bar = [&](int s) { return bar_base + 8u * (3 * kPairStages + 2 + s); };
+  const uint32_t drain_bar = bar_base + 8u * (3 * kPairStages + 4);
+  const int slot_off = 8 * (3 * kPairStages + 5);
+  const uint32_t tmem_slot = bar_base + slot_off;
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(staging_gen + kStagingBytes + slot_off);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(staging_gen + kStagingBytes + slot_off + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = static_cast<int>(cluster_cta_rank());
+  const bool leader = rank == 0;
+
+  // An earlier kernel of this pass already gave up: both CTAs of the pair leave together (the leader decides).
+  __shared__ int s_early;
+  if (threadIdx.x == 0 && leader) {
+    const uint32_t v = (p.status != nullptr && p.status->code != 0) ? 1u : 0u;
+    s_early = static_cast<int>(v);
+    st_shared_cluster_u32(map_to_cta(smem_u32(&s_early), 1), v);
+  }
+  cluster_sync_all();
+  if (s_early) return;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(full_bar(s), kRelay ? 1 : 2);  // direct scheme: one expect_tx arrival from each CTA of the pair
+      mbar_init(empty_bar(s), 1);
+      mbar_init(ready_bar(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(acc_full_bar(s), 1);
+      mbar_init(acc_empty_bar(s), 8);  // four epilogue warps in each CTA of the pair
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    mbar_init_fence();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anyone signals across the pair
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_gen;
+
+  const int num_entries = (MODE == kModeTgmm) ? p.plan[p.lay.off_num_gtiles + p.slice]
+                                              : p.plan[p.lay.off_num_ptiles + p.slice];
+  const int num_tiles = (MODE == kModeTgmm) ? num_entries * (p.m_tiles / 2) * p.n_tiles : num_entries * p.n_tiles;
+  const int first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ================================ TMA producer (both CTAs) ==============================
+    uint32_t it = 0;
+    int waited_expert = -1;
+    for (int t = first_tile; t < num_tiles && !*abort_flag; t += tile_step) {
+      const Tile tl = decode_pair_tile<MODE>(p, t, num_entries, rank);
+      if constexpr (MODE == kModeSwiglu) {
+        if (p.arrive != nullptr && tl.g != waited_expert) {
+          bool ok = true;
+          uint32_t seen = 0, target = 0;
+          if (lane < p.lay.P) {
+            const int i = lane * p.lay.L + tl.g;
+            const int through = plan_clip((p.slice + 1) * p.lay.S - p.plan[p.lay.off_in_start + i], 0,
+                                          p.plan[p.lay.off_in_size + i]);
+            target = p.pass_base[i] + static_cast<uint32_t>(through);
+            ok = spin_until_reached(p.arrive + i, target, p.spin_limit, &seen);
+            if (!ok) {
+              report_status(p.status, kStatusArrivalTimeout, kKernelGemm, MODE, p.slice, i, target, seen);
+              *abort_flag = 1;
+            }
+          }
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          waited_expert = tl.g;
+          fence_proxy_async_all();
+        }
+      }
+      if (lane == 0) {
+        for (int kb = 0; kb < tl.kblocks; ++kb, ++it) {
+          const int s = it % kPairStages;
+          const uint32_t ph = (it / kPairStages) & 1u;
+          if (!mbar_wait_poll(empty_bar(s), ph ^ 1u, p.mbar_limit)) {
+            report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1100 + s, 0, 0);
+            *abort_flag = 1;
+            break;
+          }
+          const uint32_t sa = smem_base + s * kPairStageBytes;
+          const uint32_t fb = kRelay ? full_bar(s) : map_to_cta(full_bar(s), 0);
+          if (kRelay) mbar_expect_tx(fb, kPairStageBytes); else mbar_expect_tx_cluster(fb, kPairStageBytes);
+          issue_pair_kblock<MODE>(p, tl, kb, rank, &map_a, &map_b, sa, sa + kPairStageBytesA, fb);
+        }
+      }
+      __syncwarp();
+    }
+    if (lane == 0 && *abort_flag && (kRelay || leader)) {
+      for (int s = 0; s < kPairStages; ++s) {
+        if (it > static_cast<uint32_t>(s)) {
+          const uint32_t last = it - 1 - ((it - 1 - s) % kPairStages);
+          mbar_wait(full_bar(s), (last / kPairStages) & 1u, p.mbar_limit);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ================================ MMA issuer (leader) / stage relay (peer) ==============
+    constexpr uint32_t idesc = make_instr_desc_bf16(2 * kBlockM, kBlockN, Traits::kAMn, Traits::kBMn);
+    const uint32_t peer = static_cast<uint32_t>(rank ^ 1);
+    uint32_t it = 0, tcount = 0;
+    for (int t = first_tile; t < num_tiles && !*abort_flag && (kRelay || leader); t += tile_step, ++tcount) {
+      const Tile tl = decode_pair_tile<MODE>(p, t, num_entries, rank);
+      const int as = tcount & 1;
+      const uint32_t aph = (tcount >> 1) & 1u;
+      bool ok = true;
+      if (leader) {
+        if (lane == 0) {
+          ok = mbar_wait_poll(acc_empty_bar(as), aph ^ 1u, p.mbar_limit);
+          if (!ok) {
+            report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1200 + as, 0, 0);
+            *abort_flag = 1;
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        tcgen05_fence_after_sync();
+      }
+      const uint32_t tmem_d = tmem_base + as * kBlockN;
+      for (int kb = 0; kb < tl.kblocks; ++kb, ++it) {
+        const int s = it % kPairStages;
+        const uint32_t ph = (it / kPairStages) & 1u;
+        if (lane == 0) {
+          ok = mbar_wait(full_bar(s), ph, p.mbar_limit);
+          if (!ok) {
+            report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1300 + s, 0, 0);
+            *abort_flag = 1;
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        const uint32_t sa = smem_base + s * kPairStageBytes;
+        const uint32_t sb = sa + kPairStageBytesA;
+        int ksteps = kBlockK / kUmmaK;
+        if constexpr (MODE == kModeTgmm) {
+          const int valid = tl.nrows - kb * kBlockK;
+          if (valid < kBlockK) {
+            ksteps = (valid + kUmmaK - 1) / kUmmaK;
+            // Zero this CTA's rows [valid, ksteps*16) in its four 64-column chunks (2 of A, 2 of B).
+            uint8_t* ga = smem_gen + s * kPairStageBytes;
+            const int zrows = ksteps * kUmmaK - valid;
+            for (int idx = lane; idx < zrows * 4 * 8; idx += 32) {
+              const int v16 = idx & 7, line = idx >> 3;
+              const int chunk = line & 3, r = valid + (line >> 2);
+              *reinterpret_cast<int4*>(ga + chunk * 8192 + r * 128 + v16 * 16) = make_int4(0, 0, 0, 0);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+          }
+        }
+        if (!leader) {
+          // This CTA's half of the stage is in place: tell the leader.
+          if (lane == 0) mbar_arrive_cluster(map_to_cta(ready_bar(s), peer));
+          __syncwarp();
+          continue;
+        }
+        if (lane == 0 && kRelay) {
+          ok = mbar_wait_poll(ready_bar(s), ph, p.mbar_limit);
+          if (!ok) {
+            report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1400 + s, 0, 0);
+            *abort_flag = 1;
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        tcgen05_fence_after_sync();
+        if (lane == 0) {
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            if (k < ksteps) {
+              const uint64_t da = Traits::kAMn ? make_smem_desc(sa + k * 2048, 8192, 1024)
+                                               : make_smem_desc(sa + k * 32, 16, 1024);
+              const uint64_t db = Traits::kBMn ? make_smem_desc(sb + k * 2048, 8192, 1024)
+                                               : make_smem_desc(sb + k * 32, 16, 1024);
+              umma_bf16_pair(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            }
+          }
+          // The stage is free in BOTH CTAs once these MMAs have read it.
+          umma_commit_pair(empty_bar(s));
+          umma_commit_pair(map_to_cta(empty_bar(s), peer));
+        }
+        __syncwarp();
+      }
+      if (!ok) break;
+      if (leader && lane == 0) {
+        if (tl.kblocks > 0) {
+          umma_commit_pair(acc_full_bar(as));
+          umma_commit_pair(map_to_cta(acc_full_bar(as), peer));
+        } else {
+          mbar_arrive(acc_full_bar(as));  // empty group: both epilogues write zeros
+          mbar_arrive_cluster(map_to_cta(acc_full_bar(as), peer));
+        }
+      }
+      __syncwarp();
+    }
+    if (leader && lane == 0 && *abort_flag) {
+      umma_commit_pair(drain_bar);
+      mbar_wait(drain_bar, 0, p.mbar_limit);
+    }
+  } else {
+    // ================================ epilogue (both CTAs) ==================================
+    const int q = warp & 3;
+    uint8_t* stage_gen = staging_gen + (warp - 2) * 8192;
+    const uint32_t leader_acc_empty0 = map_to_cta(acc_empty_bar(0), 0);
+    uint32_t tcount = 0;
+    for (int t = first_tile; t < num_tiles && !*abort_flag; t += tile_step, ++tcount) {
+      const Tile tl = decode_pair_tile<MODE>(p, t, num_entries, rank);
+      const int as = tcount & 1;
+      const uint32_t aph = (tcount >> 1) & 1u;
+      bool ok = mbar_wait_poll(acc_full_bar(as), aph, p.mbar_limit);
+      if (!ok) {
+        report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1500 + as, 0, 0);
+        *abort_flag = 1;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after_sync();
+      const uint32_t tacc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * kBlockN;
+      run_epilogue<MODE>(p, tl, tacc, q, lane, stage_gen);
+      tcgen05_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(leader_acc_empty0 + 8u * as);
+    }
+  }
+
+  // ================================ teardown ================================================
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // nobody frees TMEM or leaves while its partner may still signal or compute
+  if (warp == 1) {
+    tcgen05_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+// Largest persistent grid whose clusters are all resident at once. A cluster needs both SMs of one TPC free,
+// so this can be fewer than SM-count / 2 clusters; a cluster that does not fit would only start after the first
+// wave has finished ALL of its (statically assigned) tiles and double the kernel's time.
+template <typename Kernel>
+int resident_pair_grid(Kernel kernel, int requested) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(requested), 1, 1);
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = kGemmSmemBytes;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess || clusters <= 0) {
+    cudaGetLastError();
+    return requested;
+  }
+  const int grid = 2 * clusters;
+  return grid < requested ? grid : requested;
+}
+
+}  // namespace
+
+int g_pair_grid_used = 0;  // last pair grid size, for diagnostics
+
+void launch_grouped_gemm_pair(int mode, const GemmParams& p, const CUtensorMap& map_a, const CUtensorMap& map_b,
+                              int grid, cudaStream_t stream) {
+  grid &= ~1;  // whole pairs only
+#define CEM_LAUNCH_PAIR(M)                                                                                       \
+  case M: {                                                                                                      \
+    static int resident = 0;                                                                                     \
+    if (resident == 0) {                                                                                         \
+      cudaFuncSetAttribute(grouped_gemm_pair_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
+                           kGemmSmemBytes);                                                                      \
+      resident = resident_pair_grid(grouped_gemm_pair_kernel<M>, grid);                                          \
+    }                                                                                                            \
+    const int g = grid < resident ? grid : resident;                                                             \
+    g_pair_grid_used = g;                                                                                        \
+    grouped_gemm_pair_kernel<M><<<g, kGemmThreads, kGemmSmemBytes, stream>>>(p, map_a, map_b);                   \
+    break;                                                                                                       \
+  }
+  switch (mode) {
+    CEM_LAUNCH_PAIR(kModeSwiglu)
+    CEM_LAUNCH_PAIR(kModeDownFwd)
+    CEM_LAUNCH_PAIR(kModeDownDw)
+    CEM_LAUNCH_PAIR(kModeDswiglu)
+    CEM_LAUNCH_PAIR(kModeDx)
+    CEM_LAUNCH_PAIR(kModeTgmm)
+    default:
+      break;
+  }
+#undef CEM_LAUNCH_PAIR
+}
+
+}  // namespace cem

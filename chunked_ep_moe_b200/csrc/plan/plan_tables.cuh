@@ -18,6 +18,7 @@
 //   expert_start[L], expert_rows[L]   my experts in my stream
 //   per slice j:  num_mtiles[j], num_gtiles[j], num_chunks[j]
 //                 mtiles[j][max_mtiles]  {expert, row0 (slice-relative), nrows, 0}         GEMM row tiles
+//                 ptiles[j][max_ptiles]  {expert, row0, nrows (<= 256), 0}                 row-tile PAIRS (2-CTA GEMMs)
 //                 gtiles[j][max_gtiles]  {expert, row0, nrows, flags}                      weight-grad groups
 //                 put[j][P*L]            {send-order offset, rows, dest row, chunk prefix} my outgoing segments
 #pragma once
@@ -41,11 +42,11 @@ constexpr int kGroupFirst = 1;  // the expert's rows begin in this slice: overwr
 constexpr int kGroupFinal = 2;  // the expert's rows end in this slice: write the final gradient
 
 struct PlanLayout {
-  int P, L, S, max_slices, max_mtiles, max_gtiles;
+  int P, L, S, max_slices, max_mtiles, max_gtiles, max_ptiles;
   int off_send_start, off_seg_start, off_seg_size, off_in_start, off_in_size, off_src_send_start;
   int off_expert_start, off_expert_rows;
-  int off_num_mtiles, off_num_gtiles, off_num_chunks;
-  int off_mtiles, off_gtiles, off_put;
+  int off_num_mtiles, off_num_gtiles, off_num_chunks, off_num_ptiles;
+  int off_mtiles, off_gtiles, off_put, off_ptiles;
   int total;
 };
 
@@ -56,6 +57,7 @@ CEM_HD inline PlanLayout make_plan_layout(int P, int L, int S, int max_slices) {
   y.P = P; y.L = L; y.S = S; y.max_slices = max_slices;
   y.max_mtiles = (S + kTileM - 1) / kTileM + L;
   y.max_gtiles = L;
+  y.max_ptiles = (S + 2 * kTileM - 1) / (2 * kTileM) + L;
   const int n = P * L;
   int o = kPlanHeaderInts;
   y.off_send_start = o; o += plan_align4(n);
@@ -69,9 +71,11 @@ CEM_HD inline PlanLayout make_plan_layout(int P, int L, int S, int max_slices) {
   y.off_num_mtiles = o; o += plan_align4(max_slices);
   y.off_num_gtiles = o; o += plan_align4(max_slices);
   y.off_num_chunks = o; o += plan_align4(max_slices);
+  y.off_num_ptiles = o; o += plan_align4(max_slices);
   y.off_mtiles = o; o += 4 * y.max_mtiles * max_slices;
   y.off_gtiles = o; o += 4 * y.max_gtiles * max_slices;
   y.off_put = o; o += 4 * n * max_slices;
+  y.off_ptiles = o; o += 4 * y.max_ptiles * max_slices;
   y.total = o;
   return y;
 }
@@ -147,11 +151,12 @@ CEM_HD inline void plan_phase_b(int* plan, const PlanLayout& y, int tid, int nth
   int num_slices = plan[0];
   if (num_slices > y.max_slices) num_slices = y.max_slices;
   for (int j = tid; j < y.max_slices; j += nthreads) {
-    int num_m = 0, num_g = 0, chunks = 0;
+    int num_m = 0, num_g = 0, num_p = 0, chunks = 0;
     if (j < num_slices) {
       const int lo = j * S, hi = lo + S;
       int* mt = plan + y.off_mtiles + 4 * y.max_mtiles * j;
       int* gt = plan + y.off_gtiles + 4 * y.max_gtiles * j;
+      int* pt = plan + y.off_ptiles + 4 * y.max_ptiles * j;
       for (int l = 0; l < L; ++l) {
         const int es = plan[y.off_expert_start + l], er = plan[y.off_expert_rows + l];
         const int first = plan_clip(lo, es, es + er), last = plan_clip(hi, es, es + er);
@@ -163,6 +168,15 @@ CEM_HD inline void plan_phase_b(int* plan, const PlanLayout& y, int tid, int nth
             mt[4 * num_m + 2] = rows - off < kTileM ? rows - off : kTileM;
             mt[4 * num_m + 3] = 0;
             ++num_m;
+          }
+          // Pairs of consecutive row tiles of one expert share its weights in a 2-CTA MMA; an odd
+          // last tile is a pair whose second half is empty.
+          for (int off = 0; off < rows; off += 2 * kTileM) {
+            pt[4 * num_p + 0] = l;
+            pt[4 * num_p + 1] = first - lo + off;
+            pt[4 * num_p + 2] = rows - off < 2 * kTileM ? rows - off : 2 * kTileM;
+            pt[4 * num_p + 3] = 0;
+            ++num_p;
           }
           gt[4 * num_g + 0] = l;
           gt[4 * num_g + 1] = first - lo;
@@ -192,6 +206,7 @@ CEM_HD inline void plan_phase_b(int* plan, const PlanLayout& y, int tid, int nth
     plan[y.off_num_mtiles + j] = num_m;
     plan[y.off_num_gtiles + j] = num_g;
     plan[y.off_num_chunks + j] = chunks;
+    plan[y.off_num_ptiles + j] = num_p;
   }
 }
 

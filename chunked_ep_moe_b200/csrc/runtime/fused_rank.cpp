@@ -3,6 +3,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <sstream>
 #include <stdexcept>
@@ -78,9 +79,10 @@ ArenaLayout make_arena_layout(int P, int L, int S, int D, int tk_cap, bool fp8) 
 
 FusedRank::FusedRank(int P, int L, int me, int S, int D, int F, int K, int stripe, int tk_cap, int max_slices,
                      int num_sms, bool fp8, int64_t arena, std::vector<int64_t> peer_arenas, bool use_comm_stream,
-                     int64_t spin_limit, int put_blocks)
+                     int64_t spin_limit, int put_blocks, bool cta_pairs)
     : P_(P), L_(L), me_(me), S_(S), D_(D), F_(F), K_(K), stripe_(stripe), tk_cap_(tk_cap), max_slices_(max_slices),
-      num_sms_(num_sms), put_blocks_(put_blocks), fp8_(fp8), use_comm_stream_(use_comm_stream) {
+      num_sms_(num_sms), put_blocks_(put_blocks), fp8_(fp8), use_comm_stream_(use_comm_stream),
+      cta_pairs_(cta_pairs && num_sms >= 2) {
   expect(P >= 1 && L >= 1 && me >= 0 && me < P, "bad rank geometry");
   expect(static_cast<int>(peer_arenas.size()) == P, "need one arena pointer per rank");
   expect(P <= 32, "at most 32 expert-parallel ranks (one warp lane watches one source)");
@@ -91,7 +93,7 @@ FusedRank::FusedRank(int P, int L, int me, int S, int D, int F, int K, int strip
   expect(S % 8 == 0 && S >= 8, "fused kernels need slice_size % 8 == 0");
   expect(!fp8 || D % 128 == 0, "fp8 wire needs D % 128 == 0");
   spin_limit_ = static_cast<uint32_t>(spin_limit);
-  mbar_limit_ = 1u << 28;
+  mbar_limit_ = 20u * 1000u * 1000u;  // microseconds: longer than any legitimate wait on another rank
   lay_ = make_plan_layout(P, L, S, max_slices);
   arena_lay_ = make_arena_layout(P, L, S, D, tk_cap, fp8);
   arena_ = reinterpret_cast<uint8_t*>(arena);
@@ -348,7 +350,8 @@ void FusedRank::dequant(const int* plan, int j, int b, bool with_g, cudaStream_t
 
 void FusedRank::launch_gemm(int mode, const GemmParams& p, const CUtensorMap& a, const CUtensorMap& b,
                             cudaStream_t st) {
-  launch_grouped_gemm(mode, p, a, b, num_sms_, st);
+  if (cta_pairs_) launch_grouped_gemm_pair(mode, p, a, b, num_sms_, st);
+  else launch_grouped_gemm(mode, p, a, b, num_sms_, st);
   ++launches_;
 }
 
@@ -448,7 +451,7 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
     p.in0 = reinterpret_cast<const __nv_bfloat16*>(h_.data_ptr());
     p.out0 = reinterpret_cast<__nv_bfloat16*>(dh_.data_ptr());
     p.ld0 = 2 * F_;
-    launch_gemm(kModeDswiglu, p, map_dy_k_, weight_map(w_down, 256), st);
+    launch_gemm(kModeDswiglu, p, map_dy_k_, weight_map(w_down, cta_pairs_ ? 128 : 256), st);
   }
   {  // dW_down[g] = act^T dy
     GemmParams p = base_params(pl, static_cast<int>(j));
@@ -470,7 +473,7 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
     p.ld0 = D_;
     p.dwp = dwp_.data_ptr<float>();
     p.dwp_tiles = dwp_tiles;
-    launch_gemm(kModeDx, p, map_dh_k_, weight_map(w_up, 256), st);
+    launch_gemm(kModeDx, p, map_dh_k_, weight_map(w_up, cta_pairs_ ? 128 : 256), st);
   }
   {  // dW_up[g] = x^T dh
     GemmParams p = base_params(pl, static_cast<int>(j));

@@ -37,7 +37,7 @@ class FusedRank {
  public:
   FusedRank(int P, int L, int me, int S, int D, int F, int K, int stripe, int tk_cap, int max_slices, int num_sms,
             bool fp8, int64_t arena, std::vector<int64_t> peer_arenas, bool use_comm_stream, int64_t spin_limit,
-            int put_blocks);
+            int put_blocks, bool cta_pairs);
   ~FusedRank();
 
   // Forward pass set-up: sort, traffic exchange, plan tables, arrival targets. `plan`, `order`,
@@ -77,7 +77,7 @@ class FusedRank {
   void launch_gemm(int mode, const GemmParams& p, const CUtensorMap& a, const CUtensorMap& b, cudaStream_t st);
 
   int P_, L_, me_, S_, D_, F_, K_, stripe_, tk_cap_, max_slices_, num_sms_, put_blocks_;
-  bool fp8_, use_comm_stream_;
+  bool fp8_, use_comm_stream_, cta_pairs_;
   uint32_t spin_limit_, mbar_limit_;
   PlanLayout lay_;
   ArenaLayout arena_lay_;

@@ -19,6 +19,7 @@ Only the inputs and the integer plan (tables, send order, its inverse) are kept 
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -56,7 +57,8 @@ class FusedWorkspace:
             P=self.world, L=self.local_experts, me=self.rank_index, S=cfg.slice_size, D=hidden, F=ffn, K=cfg.top_k,
             stripe=cfg.stripe_width, tk_cap=tk_cap, max_slices=self.max_slices, num_sms=cfg.num_sms, fp8=self.fp8,
             arena=self.arena.local, peer_arenas=self.arena.peers, use_comm_stream=True,
-            spin_limit=_DEFAULT_SPIN_LIMIT, put_blocks=_PUT_BLOCKS)
+            spin_limit=_DEFAULT_SPIN_LIMIT, put_blocks=_PUT_BLOCKS,
+            cta_pairs=os.environ.get("CEM_CTA_PAIRS", "0") != "0")
         self.plan_ints = self.rank.plan_ints()
         self.dummy_counts = torch.zeros(1, dtype=torch.int32, device="cuda")
 

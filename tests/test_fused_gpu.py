@@ -101,7 +101,8 @@ def test_single_rank_layer_matches_oracle(group_rows, slice_size, stripe):
     _close(ds.grad.cpu(), want["dw_down"], "dw_down")
 
 
-def test_nan_poisoned_padding_does_not_leak():
+@pytest.mark.parametrize("cta_pairs", [True, False], ids=["pairs", "single"])
+def test_nan_poisoned_padding_does_not_leak(cta_pairs):
     """Scratch and slice buffers full of NaN patterns: rows outside a group must never reach an output."""
     from chunked_ep_moe_b200 import _build
     from chunked_ep_moe_b200.parallel.lockstep import LockstepWorld
@@ -114,7 +115,7 @@ def test_nan_poisoned_padding_does_not_leak():
     T = ids.shape[0]
     cfg = ChunkedMoEConfig(num_experts=E, top_k=K, slice_size=S, transport="nvshmem", expert_compute="fused",
                            stripe_width=stripe)
-    world = LockstepWorld(cfg, 1, D, F, T)
+    world = LockstepWorld(cfg, 1, D, F, T, cta_pairs=cta_pairs)
     lay = ext.arena_layout(1, E, S, D, T * K, False)
     ext.arena_fill(world.arenas.bases[0] + lay["xbuf"], lay["xq"] - lay["xbuf"], 0xFF)  # x, g, w slice buffers
     ext.arena_fill(world.arenas.bases[0] + lay["ret"], lay["arrive"] - lay["ret"], 0xFF)
@@ -138,9 +139,10 @@ def test_nan_poisoned_padding_does_not_leak():
     world.close()
 
 
+@pytest.mark.parametrize("cta_pairs", [True, False], ids=["pairs", "single"])
 @pytest.mark.parametrize("world_size,skew,slice_size", [(2, "uniform", 128), (4, "uniform", 64), (4, "all_one", 64),
                                                         (4, "rank0", 256), (8, "uniform", 2048)])
-def test_lockstep_multi_rank_matches_oracle(world_size, skew, slice_size):
+def test_lockstep_multi_rank_matches_oracle(world_size, skew, slice_size, cta_pairs):
     from chunked_ep_moe_b200.parallel.lockstep import LockstepWorld
 
     T, E, K, D, F, stripe = 48, 16, 4, 256, 256, 64
@@ -155,7 +157,7 @@ def test_lockstep_multi_rank_matches_oracle(world_size, skew, slice_size):
     wl = [sh(weights, r).cuda() for r in range(world_size)]
     ups = [bf(sh(w_up, r)) for r in range(world_size)]
     downs = [bf(sh(w_down, r)) for r in range(world_size)]
-    world = LockstepWorld(cfg, world_size, D, F, T)
+    world = LockstepWorld(cfg, world_size, D, F, T, cta_pairs=cta_pairs)
     outs, saved = world.forward(xs, idl, wl, ups, downs)
     dxs, dws, dw_ups, dw_downs = world.backward(xs, gs, ups, downs, saved)
     torch.cuda.synchronize()

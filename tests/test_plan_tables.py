@@ -72,6 +72,15 @@ def test_tables_match_torch_planner(P, L, S, skew):
                 assert row0 == starts[e] + covered[e]
                 covered[e] += nrows
             np.testing.assert_array_equal(covered, groups if j < ref.num_slices else 0 * groups)
+            # row-tile pairs (2-CTA GEMMs): same coverage in 256-row steps
+            num_p = tab[lay["num_ptiles"] + j]
+            pt = tab[lay["ptiles"] + 4 * lay["max_ptiles"] * j:][: 4 * num_p].reshape(num_p, 4)
+            covered_p = np.zeros(L, dtype=np.int64)
+            for e, row0, nrows, _ in pt:
+                assert 0 < nrows <= 2 * lay["tile_m"]
+                assert row0 == starts[e] + covered_p[e]
+                covered_p[e] += nrows
+            np.testing.assert_array_equal(covered_p, covered)
             # weight-gradient groups: one per expert present; first/final flags; empty experts once in slice 0
             num_g = tab[lay["num_gtiles"] + j]
             gt = tab[lay["gtiles"] + 4 * lay["max_gtiles"] * j:][: 4 * num_g].reshape(num_g, 4)
