@@ -152,7 +152,12 @@ FusedRank::FusedRank(int P, int L, int me, int S, int D, int F, int K, int strip
   map_dh_k_ = make_bf16_map_2d(dh_.data_ptr(), S, 2 * F, 128);
   map_dh_mn_ = make_bf16_map_2d(dh_.data_ptr(), S, 2 * F, 64);
 
-  if (use_comm_stream_) cuda_check(cudaStreamCreateWithFlags(&comm_stream_, cudaStreamNonBlocking), "comm stream");
+  if (use_comm_stream_) {
+    cuda_check(cudaStreamCreateWithFlags(&comm_stream_, cudaStreamNonBlocking), "comm stream");
+    cuda_check(cudaStreamCreateWithFlags(&aux_stream_, cudaStreamNonBlocking), "aux stream");
+  }
+  for (cudaEvent_t* e : {&ev_dw_, &ev_dsw_, &ev_tgd_, &ev_aux_done_})
+    cuda_check(cudaEventCreateWithFlags(e, cudaEventDisableTiming), "event");
   cuda_check(cudaEventCreateWithFlags(&ev_pass_, cudaEventDisableTiming), "event");
   for (int i = 0; i < 4; ++i) {
     cuda_check(cudaEventCreateWithFlags(&ev_put_[i], cudaEventDisableTiming), "event");
@@ -164,6 +169,9 @@ FusedRank::FusedRank(int P, int L, int me, int S, int D, int F, int K, int strip
 
 FusedRank::~FusedRank() {
   if (comm_stream_) cudaStreamDestroy(comm_stream_);
+  if (aux_stream_) cudaStreamDestroy(aux_stream_);
+  for (cudaEvent_t e : {ev_dw_, ev_dsw_, ev_tgd_, ev_aux_done_})
+    if (e) cudaEventDestroy(e);
   if (ev_pass_) cudaEventDestroy(ev_pass_);
   for (int i = 0; i < 4; ++i) {
     if (ev_put_[i]) cudaEventDestroy(ev_put_[i]);
@@ -416,6 +424,10 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
   const int* pl = plan.data_ptr<int>();
   const int par = static_cast<int>(j & 1);
   const int dwp_tiles = D_ / kBlockN;
+  // Weight-gradient GEMMs run on an auxiliary stream: each is independent of the kernel that precedes it in
+  // time, so its CTAs fill the SMs that kernel's last wave leaves idle. Scratch reuse is ordered by events.
+  cudaStream_t aux = use_comm_stream_ ? aux_stream_ : st;
+  if (use_comm_stream_ && j > 0) cuda_check(cudaStreamWaitEvent(st, ev_tgd_, 0), "wait dW_down event");  // act, dy reuse
   if (fp8_) dequant(pl, static_cast<int>(j), b, /*with_g=*/true, st);
   {  // remat: act and h
     GemmParams p = base_params(pl, static_cast<int>(j));
@@ -443,6 +455,10 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
     p.dwp_tiles = dwp_tiles;
     launch_gemm(kModeDownDw, p, map_act_k_, weight_map(w_down, 64), st);
   }
+  if (use_comm_stream_) {
+    cuda_check(cudaEventRecord(ev_dw_, st), "event record");
+    if (j > 0) cuda_check(cudaStreamWaitEvent(st, ev_aux_done_, 0), "wait dW_up event");  // dh reuse
+  }
   {  // dh = SwiGLU'(h) * (dy Wd^T)
     GemmParams p = base_params(pl, static_cast<int>(j));
     p.n_tiles = F_ / kBlockN;
@@ -453,6 +469,10 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
     p.ld0 = 2 * F_;
     launch_gemm(kModeDswiglu, p, map_dy_k_, weight_map(w_down, cta_pairs_ ? 128 : 256), st);
   }
+  if (use_comm_stream_) {
+    cuda_check(cudaEventRecord(ev_dsw_, st), "event record");
+    cuda_check(cudaStreamWaitEvent(aux, ev_dw_, 0), "wait down event");
+  }
   {  // dW_down[g] = act^T dy
     GemmParams p = base_params(pl, static_cast<int>(j));
     p.m_tiles = F_ / kBlockM;
@@ -460,7 +480,11 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
     p.carry_in = carry_down_.data_ptr<float>() + static_cast<size_t>(par ^ 1) * F_ * D_;
     p.carry_out = carry_down_.data_ptr<float>() + static_cast<size_t>(par) * F_ * D_;
     p.grad_out = reinterpret_cast<__nv_bfloat16*>(dw_down.data_ptr());
-    launch_gemm(kModeTgmm, p, map_act_mn_, map_dy_mn_, st);
+    launch_gemm(kModeTgmm, p, map_act_mn_, map_dy_mn_, aux);
+  }
+  if (use_comm_stream_) {
+    cuda_check(cudaEventRecord(ev_tgd_, aux), "event record");
+    cuda_check(cudaStreamWaitEvent(aux, ev_dsw_, 0), "wait dswiglu event");
   }
   {  // dx = dh Wu^T, rows and d_weight go back to their source rank
     GemmParams p = base_params(pl, static_cast<int>(j));
@@ -482,11 +506,15 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
     p.carry_in = carry_up_.data_ptr<float>() + static_cast<size_t>(par ^ 1) * D_ * 2 * F_;
     p.carry_out = carry_up_.data_ptr<float>() + static_cast<size_t>(par) * D_ * 2 * F_;
     p.grad_out = reinterpret_cast<__nv_bfloat16*>(dw_up.data_ptr());
-    launch_gemm(kModeTgmm, p, map_x_mn_[b], map_dh_mn_, st);
+    launch_gemm(kModeTgmm, p, map_x_mn_[b], map_dh_mn_, aux);
   }
-  launch_slice_done(table<uint32_t>(kTabCredit), P_, me_, seq, st);
+  launch_slice_done(table<uint32_t>(kTabCredit), P_, me_, seq, aux);
   ++launches_;
-  if (use_comm_stream_) cuda_check(cudaEventRecord(ev_done_[j % 4], st), "event record");
+  if (use_comm_stream_) {
+    cuda_check(cudaEventRecord(ev_done_[j % 4], aux), "event record");
+    cuda_check(cudaEventRecord(ev_aux_done_, aux), "event record");
+    bwd_aux_pending_ = true;
+  }
 }
 
 void FusedRank::end_pass(int64_t n_slices) {
@@ -521,6 +549,10 @@ void FusedRank::finish_backward(torch::Tensor inv_order, torch::Tensor dx, torch
              d_weights.numel() == cur_rows_,
          "d_weights must be a contiguous CUDA fp32 tensor of T*K elements");
   expect_i32(inv_order, cur_rows_, "inv_order");
+  if (bwd_aux_pending_) {  // weight gradients and credits were issued on the auxiliary stream
+    cuda_check(cudaStreamWaitEvent(current_stream(), ev_aux_done_, 0), "wait aux stream");
+    bwd_aux_pending_ = false;
+  }
   CombineParams c{};
   c.rows = reinterpret_cast<const __nv_bfloat16*>(arena_ + arena_lay_.ret);
   c.inv_order = inv_order.data_ptr<int>();

@@ -96,7 +96,9 @@ class FusedRank {
   CUtensorMap map_x_k_[2], map_x_mn_[2], map_act_k_, map_act_mn_, map_dy_k_, map_dy_mn_, map_dh_k_, map_dh_mn_;
   std::map<std::pair<const void*, uint32_t>, CUtensorMap> weight_maps_;
 
-  cudaStream_t comm_stream_ = nullptr;
+  cudaStream_t comm_stream_ = nullptr, aux_stream_ = nullptr;
+  cudaEvent_t ev_dw_ = nullptr, ev_dsw_ = nullptr, ev_tgd_ = nullptr, ev_aux_done_ = nullptr;
+  bool bwd_aux_pending_ = false;
   cudaEvent_t ev_pass_ = nullptr, ev_put_[4] = {}, ev_done_[4] = {};
   int32_t* host_header_ = nullptr;  // pinned: 16 plan header ints + 8 status ints
 

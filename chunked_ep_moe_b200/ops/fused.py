@@ -34,16 +34,22 @@ _PUT_BLOCKS = 32
 
 _workspaces: dict = {}
 
+#: Pass as `group` to run the fused kernels on this rank alone (a 1-rank expert-parallel world), whatever
+#: process groups exist. Used by `ops.fused_expert` to serve `expert_compute="fused"` on collective transports.
+SOLO = "solo"
+
 
 class FusedWorkspace:
     """Symmetric arena + per-rank executor for one (geometry, process group)."""
 
     def __init__(self, cfg: ChunkedMoEConfig, group, hidden: int, ffn: int, tk_cap: int):
         ext = _build.load()
-        initialised = dist.is_available() and dist.is_initialized()
+        initialised = dist.is_available() and dist.is_initialized() and group is not SOLO
         self.world = dist.get_world_size(group) if initialised else 1
         self.rank_index = dist.get_rank(group) if initialised else 0
         self.local_experts = cfg.num_experts // self.world
+        if group is SOLO:
+            group = None
         if self.world > 1:  # the arena layout must be identical everywhere: agree on the capacity
             cap = torch.tensor([tk_cap], device="cuda", dtype=torch.int64)
             dist.all_reduce(cap, op=dist.ReduceOp.MAX, group=group)
@@ -52,19 +58,19 @@ class FusedWorkspace:
         self.fp8 = cfg.comm_dtype == "float8_e4m3fn"
         self.max_slices = max(1, math.ceil(self.world * tk_cap / cfg.slice_size)) + 1
         nbytes = ext.arena_bytes(self.world, self.local_experts, cfg.slice_size, hidden, tk_cap, self.fp8)
-        self.arena = SymmetricArena(nbytes, group)
+        self.arena = SymmetricArena(nbytes, group, solo=self.world == 1)
         self.rank = ext.FusedRank(
             P=self.world, L=self.local_experts, me=self.rank_index, S=cfg.slice_size, D=hidden, F=ffn, K=cfg.top_k,
             stripe=cfg.stripe_width, tk_cap=tk_cap, max_slices=self.max_slices, num_sms=cfg.num_sms, fp8=self.fp8,
             arena=self.arena.local, peer_arenas=self.arena.peers, use_comm_stream=True,
-            spin_limit=_DEFAULT_SPIN_LIMIT, put_blocks=_PUT_BLOCKS,
+            spin_limit=_DEFAULT_SPIN_LIMIT, put_blocks=int(os.environ.get("CEM_PUT_BLOCKS", _PUT_BLOCKS)),
             cta_pairs=os.environ.get("CEM_CTA_PAIRS", "0") != "0")
         self.plan_ints = self.rank.plan_ints()
         self.dummy_counts = torch.zeros(1, dtype=torch.int32, device="cuda")
 
 
 def get_workspace(cfg: ChunkedMoEConfig, group, hidden: int, ffn: int, tokens_times_k: int) -> FusedWorkspace:
-    key = (id(group) if group is not None else 0, cfg.num_experts, cfg.top_k, cfg.slice_size, cfg.stripe_width,
+    key = (group if group is SOLO else (id(group) if group is not None else 0), cfg.num_experts, cfg.top_k, cfg.slice_size, cfg.stripe_width,
            cfg.comm_dtype, cfg.num_sms, hidden, ffn, torch.cuda.current_device())
     ws = _workspaces.get(key)
     if ws is None or ws.tk_cap < tokens_times_k:
@@ -88,6 +94,12 @@ def launches() -> int:
     return sum(int(ws.rank.launches()) for ws in _workspaces.values() if ws.rank is not None)
 
 
+def nvtx(name: str):
+    from ..utils.nvtx import nvtx_range
+
+    return nvtx_range(name)
+
+
 def _require(cond: bool, msg: str) -> None:
     if not cond:
         raise ValueError("chunked_moe fused path: " + msg)
@@ -107,15 +119,18 @@ class _ChunkedMoEFused(torch.autograd.Function):
         ids32 = expert_ids.to(torch.int32).contiguous()
         w_flat = weights.detach().float().reshape(-1).contiguous()
         xc, w_up_c, w_down_c = x.detach().contiguous(), w_up.detach().contiguous(), w_down.detach().contiguous()
-        n = rank.begin_forward(ids32, plan, order, inv_order, ws.dummy_counts, False)
+        with nvtx("chunked_moe/plan"):
+            n = rank.begin_forward(ids32, plan, order, inv_order, ws.dummy_counts, False)
         out = torch.empty_like(xc)
         if n > 0:
             rank.put(0, plan, order, xc, None, w_flat)
         for j in range(n):
-            if j + 1 < n:
-                rank.put(j + 1, plan, order, xc, None, w_flat)  # slice j+1 is in flight while slice j computes
-            rank.compute_forward(j, plan, w_up_c, w_down_c)
-        rank.finish_forward(inv_order, out)
+            with nvtx(f"chunked_moe/fwd slice {j}"):
+                if j + 1 < n:
+                    rank.put(j + 1, plan, order, xc, None, w_flat)  # slice j+1 is in flight while slice j computes
+                rank.compute_forward(j, plan, w_up_c, w_down_c)
+        with nvtx("chunked_moe/combine"):
+            rank.finish_forward(inv_order, out)
         ctx.save_for_backward(xc, weights, w_up_c, w_down_c, plan, order, inv_order)
         ctx.cfg, ctx.group, ctx.ws = cfg, group, ws
         ctx.mark_non_differentiable(expert_ids)
@@ -135,9 +150,10 @@ class _ChunkedMoEFused(torch.autograd.Function):
             dw_up.zero_()
             dw_down.zero_()
         for j in range(n):
-            if j + 1 < n:
-                rank.put(j + 1, plan, order, x, g, w_flat)
-            rank.compute_backward(j, plan, w_up, w_down, dw_up, dw_down)
+            with nvtx(f"chunked_moe/bwd slice {j}"):
+                if j + 1 < n:
+                    rank.put(j + 1, plan, order, x, g, w_flat)
+                rank.compute_backward(j, plan, w_up, w_down, dw_up, dw_down)
         dx = torch.empty_like(x)
         d_weights = torch.empty(weights.numel(), dtype=torch.float32, device=x.device)
         rank.finish_backward(inv_order, dx, d_weights)

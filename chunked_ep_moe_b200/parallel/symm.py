@@ -22,12 +22,12 @@ from .. import _build
 class SymmetricArena:
     """This rank's arena plus the mapped base address of every peer's arena."""
 
-    def __init__(self, nbytes: int, group: Optional[dist.ProcessGroup] = None):
+    def __init__(self, nbytes: int, group: Optional[dist.ProcessGroup] = None, solo: bool = False):
         ext = _build.load()
         self._ext = ext
         self.nbytes = int(nbytes)
         self.group = group
-        initialised = dist.is_available() and dist.is_initialized()
+        initialised = dist.is_available() and dist.is_initialized() and not solo
         self.world = dist.get_world_size(group) if initialised else 1
         self.rank = dist.get_rank(group) if initialised else 0
         self.local = ext.arena_alloc(self.nbytes)

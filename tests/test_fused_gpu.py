@@ -101,6 +101,32 @@ def test_single_rank_layer_matches_oracle(group_rows, slice_size, stripe):
     _close(ds.grad.cpu(), want["dw_down"], "dw_down")
 
 
+def test_fused_expert_compute_on_a_collective_transport():
+    """`expert_compute="fused"` under `transport="ragged_a2a"`: the library exchange feeds the sm_100a kernels."""
+    gen = torch.Generator().manual_seed(4)
+    E, K, D, F, stripe, S = 4, 2, 256, 256, 64, 96
+    ids = _ids_with_groups([50, 0, 77, 33], K, E, gen)
+    T = ids.shape[0]
+    bf = lambda t: t.cuda().to(torch.bfloat16)
+    x, g = bf(torch.randn(T, D, generator=gen)), bf(torch.randn(T, D, generator=gen))
+    weights = (torch.rand(T, K, generator=gen) + 0.1).cuda()
+    w_up = bf(torch.randn(E, D, 2 * F, generator=gen) / math.sqrt(D))
+    w_down = bf(torch.randn(E, F, D, generator=gen) / math.sqrt(F))
+    cfg = ChunkedMoEConfig(num_experts=E, top_k=K, slice_size=S, transport="ragged_a2a", expert_compute="fused",
+                           stripe_width=stripe)
+    xs, ws = x.clone().requires_grad_(True), weights.clone().requires_grad_(True)
+    us, ds = w_up.clone().requires_grad_(True), w_down.clone().requires_grad_(True)
+    out = chunked_moe(xs, ids.cuda(), ws, us, ds, cfg, None)
+    out.backward(g)
+    torch.cuda.synchronize()
+    want = _oracle_dev(x, ids, weights, w_up, w_down, g, stripe)
+    _close(out.detach().cpu(), want["out"], "out")
+    _close(xs.grad.cpu(), want["dx"], "dx")
+    _close(ws.grad.cpu(), want["dweights"], "dweights")
+    _close(us.grad.cpu(), want["dw_up"], "dw_up")
+    _close(ds.grad.cpu(), want["dw_down"], "dw_down")
+
+
 @pytest.mark.parametrize("cta_pairs", [True, False], ids=["pairs", "single"])
 def test_nan_poisoned_padding_does_not_leak(cta_pairs):
     """Scratch and slice buffers full of NaN patterns: rows outside a group must never reach an output."""
