@@ -49,6 +49,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--comm-dtype", default=None, choices=[None, "float8_e4m3fn"])
     ap.add_argument("--save", default=None, help="directory to write a checkpoint to after the last step")
     ap.add_argument("--resume", default=None, help="directory to resume from")
+    ap.add_argument("--health-timeout", type=float, default=0.0,
+                    help="seconds to wait for every rank's heartbeat before each step (0 = no heartbeat)")
     ap.add_argument("--json", action="store_true", help="print one JSON summary line at the end (rank 0)")
     return ap
 
@@ -107,9 +109,17 @@ def train(args, group=None) -> dict:
     if args.resume:
         start_step = ckpt.load_checkpoint(args.resume, model, opt, rank)
 
+    health = None
+    if distributed and world > 1 and args.health_timeout > 0:
+        from .utils.health import RankHealth
+
+        health = RankHealth(dist.distributed_c10d._get_default_store(), rank, world, timeout_s=args.health_timeout)
+
     losses, step_ms = [], []
     timer = DeviceTimer()
     for step in range(start_step, start_step + args.steps):
+        if health is not None:
+            health.step_barrier(step)  # a missing peer is reported here, on the host, with nothing in flight
         timer.start()
         opt.zero_grad(set_to_none=True)
         loss_sum = torch.zeros((), device=device)
