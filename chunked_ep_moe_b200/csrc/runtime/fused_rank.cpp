@@ -321,7 +321,9 @@ GemmParams FusedRank::base_params(const int* plan, int j) const {
 }
 
 const CUtensorMap& FusedRank::weight_map(const torch::Tensor& w, uint32_t box_rows) {
-  auto key = std::make_pair(static_cast<const void*>(w.data_ptr()), box_rows);
+  // Keyed by address AND geometry: a freed tensor's address can come back with another shape.
+  auto key = std::make_tuple(static_cast<const void*>(w.data_ptr()), box_rows,
+                             static_cast<int64_t>(w.size(0)) * w.size(1), static_cast<int64_t>(w.size(2)));
   auto it = weight_maps_.find(key);
   if (it == weight_maps_.end()) {
     if (weight_maps_.size() > 4096) weight_maps_.clear();

@@ -18,6 +18,7 @@
 
 #include <map>
 #include <string>
+#include <tuple>
 #include <vector>
 
 #include "../comm/comm_kernels.cuh"
@@ -94,7 +95,7 @@ class FusedRank {
   T* const* table(int t) const { return reinterpret_cast<T* const*>(tables_.data_ptr<int64_t>() + t * P_); }
 
   CUtensorMap map_x_k_[2], map_x_mn_[2], map_act_k_, map_act_mn_, map_dy_k_, map_dy_mn_, map_dh_k_, map_dh_mn_;
-  std::map<std::pair<const void*, uint32_t>, CUtensorMap> weight_maps_;
+  std::map<std::tuple<const void*, uint32_t, int64_t, int64_t>, CUtensorMap> weight_maps_;
 
   cudaStream_t comm_stream_ = nullptr, aux_stream_ = nullptr;
   cudaEvent_t ev_dw_ = nullptr, ev_dsw_ = nullptr, ev_tgd_ = nullptr, ev_aux_done_ = nullptr;
