@@ -184,13 +184,33 @@ def main():
         out.backward(g_d)
         return out, x.grad, weights.grad
 
+    # End-to-end step: this step's inputs come from pinned host memory (copied on a side stream while the previous
+    # step computes, double buffered) and the step's scalar result is read back to the host before the step ends.
+    copy_stream = torch.cuda.Stream(device=dev)
+    staged = [None, None]
+
+    def stage_inputs(slot):
+        with torch.cuda.stream(copy_stream):
+            staged[slot] = (x_h.to(dev, non_blocking=True), ids_h.to(dev, non_blocking=True),
+                            weights_h.to(dev, non_blocking=True), torch.cuda.Event())
+            staged[slot][3].record(copy_stream)
+
+    e2e_count = [0]
+
     def step_e2e():
-        x = x_h.to(dev, non_blocking=True)
-        ids = ids_h.to(dev, non_blocking=True)
-        weights = weights_h.to(dev, non_blocking=True)
+        slot = e2e_count[0] & 1
+        if staged[slot] is None:
+            stage_inputs(slot)
+        x, ids, weights, ready = staged[slot]
+        staged[slot] = None
+        torch.cuda.current_stream().wait_event(ready)
+        for t in (x, ids, weights):
+            t.record_stream(torch.cuda.current_stream())
+        stage_inputs(slot ^ 1)  # the next step's copy overlaps this step's compute
         out, dx, dw = step(x, ids, weights)
         loss_h.copy_((out.float().mean() + dx.float().mean()).reshape(1), non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the host owns the step's result before the next step starts
+        e2e_count[0] += 1
         return float(loss_h[0])
 
     def sync_all():

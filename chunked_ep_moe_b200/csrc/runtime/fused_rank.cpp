@@ -102,11 +102,13 @@ FusedRank::FusedRank(int P, int L, int me, int S, int D, int F, int K, int strip
   auto bf16 = torch::TensorOptions().device(torch::kCUDA).dtype(torch::kBFloat16);
   auto f32 = torch::TensorOptions().device(torch::kCUDA).dtype(torch::kFloat32);
   auto i32 = torch::TensorOptions().device(torch::kCUDA).dtype(torch::kInt32);
-  act_ = torch::zeros({S, F}, bf16);
-  h_ = torch::zeros({S, 2 * F}, bf16);
-  dy_ = torch::zeros({S, D}, bf16);
-  dh_ = torch::zeros({S, 2 * F}, bf16);
-  dwp_ = torch::zeros({S, D / 256}, f32);
+  for (int q = 0; q < 2; ++q) {  // double buffered by slice parity: two slices are in flight at a time
+    act_[q] = torch::zeros({S, F}, bf16);
+    h_[q] = torch::zeros({S, 2 * F}, bf16);
+    dy_[q] = torch::zeros({S, D}, bf16);
+    dh_[q] = torch::zeros({S, 2 * F}, bf16);
+    dwp_[q] = torch::zeros({S, D / 256}, f32);
+  }
   carry_up_ = torch::zeros({2, D, 2 * F}, f32);
   carry_down_ = torch::zeros({2, F, D}, f32);
   pass_base_ = torch::zeros({P * L}, i32);
@@ -145,19 +147,23 @@ FusedRank::FusedRank(int P, int L, int me, int S, int D, int F, int K, int strip
     map_x_k_[b] = make_bf16_map_2d(xb, S, D, 128);
     map_x_mn_[b] = make_bf16_map_2d(xb, S, D, 64);
   }
-  map_act_k_ = make_bf16_map_2d(act_.data_ptr(), S, F, 128);
-  map_act_mn_ = make_bf16_map_2d(act_.data_ptr(), S, F, 64);
-  map_dy_k_ = make_bf16_map_2d(dy_.data_ptr(), S, D, 128);
-  map_dy_mn_ = make_bf16_map_2d(dy_.data_ptr(), S, D, 64);
-  map_dh_k_ = make_bf16_map_2d(dh_.data_ptr(), S, 2 * F, 128);
-  map_dh_mn_ = make_bf16_map_2d(dh_.data_ptr(), S, 2 * F, 64);
+  for (int q = 0; q < 2; ++q) {
+    map_act_k_[q] = make_bf16_map_2d(act_[q].data_ptr(), S, F, 128);
+    map_act_mn_[q] = make_bf16_map_2d(act_[q].data_ptr(), S, F, 64);
+    map_dy_k_[q] = make_bf16_map_2d(dy_[q].data_ptr(), S, D, 128);
+    map_dy_mn_[q] = make_bf16_map_2d(dy_[q].data_ptr(), S, D, 64);
+    map_dh_k_[q] = make_bf16_map_2d(dh_[q].data_ptr(), S, 2 * F, 128);
+    map_dh_mn_[q] = make_bf16_map_2d(dh_[q].data_ptr(), S, 2 * F, 64);
+  }
 
   if (use_comm_stream_) {
     cuda_check(cudaStreamCreateWithFlags(&comm_stream_, cudaStreamNonBlocking), "comm stream");
     cuda_check(cudaStreamCreateWithFlags(&aux_stream_, cudaStreamNonBlocking), "aux stream");
+    for (int q = 0; q < 2; ++q) cuda_check(cudaStreamCreateWithFlags(&chain_[q], cudaStreamNonBlocking), "chain stream");
   }
-  for (cudaEvent_t* e : {&ev_dw_, &ev_dsw_, &ev_tgd_, &ev_aux_done_})
-    cuda_check(cudaEventCreateWithFlags(e, cudaEventDisableTiming), "event");
+  for (int q = 0; q < 2; ++q)
+    for (cudaEvent_t* e : {&ev_down_[q], &ev_dd_[q], &ev_ds_[q], &ev_dx_[q], &ev_tgd_[q], &ev_tgu_[q]})
+      cuda_check(cudaEventCreateWithFlags(e, cudaEventDisableTiming), "event");
   cuda_check(cudaEventCreateWithFlags(&ev_pass_, cudaEventDisableTiming), "event");
   for (int i = 0; i < 4; ++i) {
     cuda_check(cudaEventCreateWithFlags(&ev_put_[i], cudaEventDisableTiming), "event");
@@ -170,8 +176,11 @@ FusedRank::FusedRank(int P, int L, int me, int S, int D, int F, int K, int strip
 FusedRank::~FusedRank() {
   if (comm_stream_) cudaStreamDestroy(comm_stream_);
   if (aux_stream_) cudaStreamDestroy(aux_stream_);
-  for (cudaEvent_t e : {ev_dw_, ev_dsw_, ev_tgd_, ev_aux_done_})
-    if (e) cudaEventDestroy(e);
+  for (int q = 0; q < 2; ++q) {
+    if (chain_[q]) cudaStreamDestroy(chain_[q]);
+    for (cudaEvent_t e : {ev_down_[q], ev_dd_[q], ev_ds_[q], ev_dx_[q], ev_tgd_[q], ev_tgu_[q]})
+      if (e) cudaEventDestroy(e);
+  }
   if (ev_pass_) cudaEventDestroy(ev_pass_);
   for (int i = 0; i < 4; ++i) {
     if (ev_put_[i]) cudaEventDestroy(ev_put_[i]);
@@ -376,11 +385,22 @@ void expect_weights(const torch::Tensor& w_up, const torch::Tensor& w_down, int 
 }
 }  // namespace
 
+// Two slices are in flight at a time. Even and odd slices run their kernel chains on two streams with their own
+// scratch buffers, the weight-gradient GEMMs and the in-order credit release run on an auxiliary stream, the puts on
+// the comm stream. A persistent GEMM kernel needs a whole SM per CTA, so two ready kernels do not share SMs: the
+// later one's CTAs start as the earlier one's CTAs finish, i.e. every kernel fills the idle tail of the previous
+// (independent) one instead of waiting for it. Scratch reuse and the carry chain are ordered by events.
 void FusedRank::compute_forward(int64_t j, torch::Tensor plan, torch::Tensor w_up, torch::Tensor w_down) {
   expect(j >= 0 && j < cur_slices_, "slice index out of range");
   expect_weights(w_up, w_down, L_, D_, F_);
-  cudaStream_t st = current_stream();
-  if (use_comm_stream_) cuda_check(cudaStreamWaitEvent(st, ev_put_[j % 4], 0), "wait put event");
+  const bool async = use_comm_stream_;
+  const int q = static_cast<int>(j & 1);
+  cudaStream_t st = async ? chain_[q] : current_stream();
+  cudaStream_t aux = async ? aux_stream_ : st;
+  if (async) {
+    if (j < 2) cuda_check(cudaStreamWaitEvent(st, ev_pass_, 0), "wait pass event");
+    cuda_check(cudaStreamWaitEvent(st, ev_put_[j % 4], 0), "wait put event");
+  }
   const uint32_t seq = seq_ + static_cast<uint32_t>(j);
   const int b = static_cast<int>(seq & 1u);
   const int* pl = plan.data_ptr<int>();
@@ -392,7 +412,7 @@ void FusedRank::compute_forward(int64_t j, torch::Tensor plan, torch::Tensor w_u
     p.b_group_rows = D_;
     p.arrive = fp8_ ? nullptr : reinterpret_cast<const uint32_t*>(arena_ + arena_lay_.arrive);
     p.pass_base = reinterpret_cast<const uint32_t*>(pass_base_.data_ptr());
-    p.out0 = reinterpret_cast<__nv_bfloat16*>(act_.data_ptr());
+    p.out0 = reinterpret_cast<__nv_bfloat16*>(act_[q].data_ptr());
     p.ld0 = F_;
     p.out1 = nullptr;
     p.ld1 = 2 * F_;
@@ -407,11 +427,15 @@ void FusedRank::compute_forward(int64_t j, torch::Tensor plan, torch::Tensor w_u
     p.peer_rows = table<__nv_bfloat16>(kTabRet);
     p.peer_count = table<uint32_t>(kTabCount);
     p.ld0 = D_;
-    launch_gemm(kModeDownFwd, p, map_act_k_, weight_map(w_down, 64), st);
+    launch_gemm(kModeDownFwd, p, map_act_k_[q], weight_map(w_down, 64), st);
   }
-  launch_slice_done(table<uint32_t>(kTabCredit), P_, me_, seq, st);
+  if (async) {
+    cuda_check(cudaEventRecord(ev_down_[q], st), "event record");
+    cuda_check(cudaStreamWaitEvent(aux, ev_down_[q], 0), "wait down event");
+  }
+  launch_slice_done(table<uint32_t>(kTabCredit), P_, me_, seq, aux);  // credits leave in slice order
   ++launches_;
-  if (use_comm_stream_) cuda_check(cudaEventRecord(ev_done_[j % 4], st), "event record");
+  if (async) cuda_check(cudaEventRecord(ev_done_[j % 4], aux), "event record");
 }
 
 void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_up, torch::Tensor w_down,
@@ -419,17 +443,20 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
   expect(j >= 0 && j < cur_slices_, "slice index out of range");
   expect_weights(w_up, w_down, L_, D_, F_);
   expect_weights(dw_up, dw_down, L_, D_, F_);
-  cudaStream_t st = current_stream();
-  if (use_comm_stream_) cuda_check(cudaStreamWaitEvent(st, ev_put_[j % 4], 0), "wait put event");
+  const bool async = use_comm_stream_;
+  const int q = static_cast<int>(j & 1);
+  cudaStream_t st = async ? chain_[q] : current_stream();
+  cudaStream_t aux = async ? aux_stream_ : st;
+  if (async) {
+    if (j < 2) cuda_check(cudaStreamWaitEvent(st, ev_pass_, 0), "wait pass event");
+    cuda_check(cudaStreamWaitEvent(st, ev_put_[j % 4], 0), "wait put event");
+    if (j >= 2) cuda_check(cudaStreamWaitEvent(st, ev_tgd_[q], 0), "wait dW_down event");  // act, h, dy of slice j-2
+  }
   const uint32_t seq = seq_ + static_cast<uint32_t>(j);
   const int b = static_cast<int>(seq & 1u);
   const int* pl = plan.data_ptr<int>();
   const int par = static_cast<int>(j & 1);
   const int dwp_tiles = D_ / kBlockN;
-  // Weight-gradient GEMMs run on an auxiliary stream: each is independent of the kernel that precedes it in
-  // time, so its CTAs fill the SMs that kernel's last wave leaves idle. Scratch reuse is ordered by events.
-  cudaStream_t aux = use_comm_stream_ ? aux_stream_ : st;
-  if (use_comm_stream_ && j > 0) cuda_check(cudaStreamWaitEvent(st, ev_tgd_, 0), "wait dW_down event");  // act, dy reuse
   if (fp8_) dequant(pl, static_cast<int>(j), b, /*with_g=*/true, st);
   {  // remat: act and h
     GemmParams p = base_params(pl, static_cast<int>(j));
@@ -438,9 +465,9 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
     p.b_group_rows = D_;
     p.arrive = fp8_ ? nullptr : reinterpret_cast<const uint32_t*>(arena_ + arena_lay_.arrive);
     p.pass_base = reinterpret_cast<const uint32_t*>(pass_base_.data_ptr());
-    p.out0 = reinterpret_cast<__nv_bfloat16*>(act_.data_ptr());
+    p.out0 = reinterpret_cast<__nv_bfloat16*>(act_[q].data_ptr());
     p.ld0 = F_;
-    p.out1 = reinterpret_cast<__nv_bfloat16*>(h_.data_ptr());
+    p.out1 = reinterpret_cast<__nv_bfloat16*>(h_[q].data_ptr());
     p.ld1 = 2 * F_;
     launch_gemm(kModeSwiglu, p, map_x_k_[b], weight_map(w_up, 64), st);
   }
@@ -451,42 +478,42 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
     p.b_group_rows = F_;
     p.row_w = reinterpret_cast<const float*>(arena_ + arena_lay_.wbuf) + static_cast<size_t>(b) * S_;
     p.in0 = reinterpret_cast<const __nv_bfloat16*>(arena_ + arena_lay_.gbuf) + static_cast<size_t>(b) * S_ * D_;
-    p.out0 = reinterpret_cast<__nv_bfloat16*>(dy_.data_ptr());
+    p.out0 = reinterpret_cast<__nv_bfloat16*>(dy_[q].data_ptr());
     p.ld0 = D_;
-    p.dwp = dwp_.data_ptr<float>();
+    p.dwp = dwp_[q].data_ptr<float>();
     p.dwp_tiles = dwp_tiles;
-    launch_gemm(kModeDownDw, p, map_act_k_, weight_map(w_down, 64), st);
+    launch_gemm(kModeDownDw, p, map_act_k_[q], weight_map(w_down, 64), st);
   }
-  if (use_comm_stream_) {
-    cuda_check(cudaEventRecord(ev_dw_, st), "event record");
-    if (j > 0) cuda_check(cudaStreamWaitEvent(st, ev_aux_done_, 0), "wait dW_up event");  // dh reuse
+  if (async) {
+    cuda_check(cudaEventRecord(ev_dd_[q], st), "event record");
+    if (j >= 2) cuda_check(cudaStreamWaitEvent(st, ev_tgu_[q], 0), "wait dW_up event");  // dh of slice j-2
   }
   {  // dh = SwiGLU'(h) * (dy Wd^T)
     GemmParams p = base_params(pl, static_cast<int>(j));
     p.n_tiles = F_ / kBlockN;
     p.k_blocks = D_ / kBlockK;
     p.b_group_rows = F_;
-    p.in0 = reinterpret_cast<const __nv_bfloat16*>(h_.data_ptr());
-    p.out0 = reinterpret_cast<__nv_bfloat16*>(dh_.data_ptr());
+    p.in0 = reinterpret_cast<const __nv_bfloat16*>(h_[q].data_ptr());
+    p.out0 = reinterpret_cast<__nv_bfloat16*>(dh_[q].data_ptr());
     p.ld0 = 2 * F_;
-    launch_gemm(kModeDswiglu, p, map_dy_k_, weight_map(w_down, cta_pairs_ ? 128 : 256), st);
+    launch_gemm(kModeDswiglu, p, map_dy_k_[q], weight_map(w_down, cta_pairs_ ? 128 : 256), st);
   }
-  if (use_comm_stream_) {
-    cuda_check(cudaEventRecord(ev_dsw_, st), "event record");
-    cuda_check(cudaStreamWaitEvent(aux, ev_dw_, 0), "wait down event");
+  if (async) {
+    cuda_check(cudaEventRecord(ev_ds_[q], st), "event record");
+    cuda_check(cudaStreamWaitEvent(aux, ev_dd_[q], 0), "wait down event");
   }
-  {  // dW_down[g] = act^T dy
+  {  // dW_down[g] = act^T dy   (auxiliary stream; the fp32 carry chains slice to slice there)
     GemmParams p = base_params(pl, static_cast<int>(j));
     p.m_tiles = F_ / kBlockM;
     p.n_tiles = D_ / kBlockN;
     p.carry_in = carry_down_.data_ptr<float>() + static_cast<size_t>(par ^ 1) * F_ * D_;
     p.carry_out = carry_down_.data_ptr<float>() + static_cast<size_t>(par) * F_ * D_;
     p.grad_out = reinterpret_cast<__nv_bfloat16*>(dw_down.data_ptr());
-    launch_gemm(kModeTgmm, p, map_act_mn_, map_dy_mn_, aux);
+    launch_gemm(kModeTgmm, p, map_act_mn_[q], map_dy_mn_[q], aux);
   }
-  if (use_comm_stream_) {
-    cuda_check(cudaEventRecord(ev_tgd_, aux), "event record");
-    cuda_check(cudaStreamWaitEvent(aux, ev_dsw_, 0), "wait dswiglu event");
+  if (async) {
+    cuda_check(cudaEventRecord(ev_tgd_[q], aux), "event record");
+    cuda_check(cudaStreamWaitEvent(aux, ev_ds_[q], 0), "wait dswiglu event");
   }
   {  // dx = dh Wu^T, rows and d_weight go back to their source rank
     GemmParams p = base_params(pl, static_cast<int>(j));
@@ -497,10 +524,11 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
     p.peer_dw = table<float>(kTabDw);
     p.peer_count = table<uint32_t>(kTabCount);
     p.ld0 = D_;
-    p.dwp = dwp_.data_ptr<float>();
+    p.dwp = dwp_[q].data_ptr<float>();
     p.dwp_tiles = dwp_tiles;
-    launch_gemm(kModeDx, p, map_dh_k_, weight_map(w_up, cta_pairs_ ? 128 : 256), st);
+    launch_gemm(kModeDx, p, map_dh_k_[q], weight_map(w_up, cta_pairs_ ? 128 : 256), st);
   }
+  if (async) cuda_check(cudaEventRecord(ev_dx_[q], st), "event record");
   {  // dW_up[g] = x^T dh
     GemmParams p = base_params(pl, static_cast<int>(j));
     p.m_tiles = D_ / kBlockM;
@@ -508,14 +536,22 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
     p.carry_in = carry_up_.data_ptr<float>() + static_cast<size_t>(par ^ 1) * D_ * 2 * F_;
     p.carry_out = carry_up_.data_ptr<float>() + static_cast<size_t>(par) * D_ * 2 * F_;
     p.grad_out = reinterpret_cast<__nv_bfloat16*>(dw_up.data_ptr());
-    launch_gemm(kModeTgmm, p, map_x_mn_[b], map_dh_mn_, aux);
+    launch_gemm(kModeTgmm, p, map_x_mn_[b], map_dh_mn_[q], aux);
   }
+  if (async) cuda_check(cudaEventRecord(ev_tgu_[q], aux), "event record");
   launch_slice_done(table<uint32_t>(kTabCredit), P_, me_, seq, aux);
   ++launches_;
-  if (use_comm_stream_) {
-    cuda_check(cudaEventRecord(ev_done_[j % 4], aux), "event record");
-    cuda_check(cudaEventRecord(ev_aux_done_, aux), "event record");
-    bwd_aux_pending_ = true;
+  if (async) cuda_check(cudaEventRecord(ev_done_[j % 4], aux), "event record");
+}
+
+// Makes the caller's stream wait for everything the pass issued on the chain and auxiliary streams.
+void FusedRank::join_streams(bool backward) {
+  if (!use_comm_stream_ || cur_slices_ <= 0) return;
+  cudaStream_t st = current_stream();
+  cuda_check(cudaStreamWaitEvent(st, ev_done_[(cur_slices_ - 1) % 4], 0), "join aux stream");
+  if (backward) {
+    cuda_check(cudaStreamWaitEvent(st, ev_dx_[(cur_slices_ - 1) & 1], 0), "join chain stream");
+    if (cur_slices_ >= 2) cuda_check(cudaStreamWaitEvent(st, ev_dx_[cur_slices_ & 1], 0), "join chain stream");
   }
 }
 
@@ -528,6 +564,7 @@ void FusedRank::finish_forward(torch::Tensor inv_order, torch::Tensor out) {
   expect_bf16_2d(out, D_, "out");
   expect(out.size(0) * K_ == cur_rows_, "out rows do not match the pass");
   expect_i32(inv_order, cur_rows_, "inv_order");
+  join_streams(/*backward=*/false);
   CombineParams c{};
   c.rows = reinterpret_cast<const __nv_bfloat16*>(arena_ + arena_lay_.ret);
   c.inv_order = inv_order.data_ptr<int>();
@@ -551,10 +588,7 @@ void FusedRank::finish_backward(torch::Tensor inv_order, torch::Tensor dx, torch
              d_weights.numel() == cur_rows_,
          "d_weights must be a contiguous CUDA fp32 tensor of T*K elements");
   expect_i32(inv_order, cur_rows_, "inv_order");
-  if (bwd_aux_pending_) {  // weight gradients and credits were issued on the auxiliary stream
-    cuda_check(cudaStreamWaitEvent(current_stream(), ev_aux_done_, 0), "wait aux stream");
-    bwd_aux_pending_ = false;
-  }
+  join_streams(/*backward=*/true);
   CombineParams c{};
   c.rows = reinterpret_cast<const __nv_bfloat16*>(arena_ + arena_lay_.ret);
   c.inv_order = inv_order.data_ptr<int>();

@@ -65,13 +65,14 @@ class FusedRank {
   int64_t plan_ints() const { return lay_.total; }
   int64_t launches() const { return launches_; }
   // Debug views of the local scratch (tests compare them with the torch reference).
-  torch::Tensor act() const { return act_; }
-  torch::Tensor h() const { return h_; }
-  torch::Tensor dh() const { return dh_; }
-  torch::Tensor dy() const { return dy_; }
+  torch::Tensor act() const { return act_[0]; }
+  torch::Tensor h() const { return h_[0]; }
+  torch::Tensor dh() const { return dh_[0]; }
+  torch::Tensor dy() const { return dy_[0]; }
 
  private:
   void end_pass(int64_t n_slices);
+  void join_streams(bool backward);
   GemmParams base_params(const int* plan, int j) const;
   const CUtensorMap& weight_map(const torch::Tensor& w, uint32_t box_rows);
   void dequant(const int* plan, int j, int b, bool with_g, cudaStream_t st);
@@ -86,7 +87,8 @@ class FusedRank {
   std::vector<uint8_t*> peers_;
 
   // local scratch (torch-owned)
-  torch::Tensor act_, h_, dy_, dh_, dwp_, carry_up_, carry_down_, pass_base_, expected_total_, status_, tables_,
+  torch::Tensor act_[2], h_[2], dy_[2], dh_[2], dwp_[2];
+  torch::Tensor carry_up_, carry_down_, pass_base_, expected_total_, status_, tables_,
       sort_scratch_, my_counts_;
   // device pointer tables, rows of `tables_`
   enum Table { kTabX, kTabG, kTabW, kTabXq, kTabGq, kTabXs, kTabGs, kTabArrive, kTabRet, kTabDw, kTabCount,
@@ -94,12 +96,12 @@ class FusedRank {
   template <typename T>
   T* const* table(int t) const { return reinterpret_cast<T* const*>(tables_.data_ptr<int64_t>() + t * P_); }
 
-  CUtensorMap map_x_k_[2], map_x_mn_[2], map_act_k_, map_act_mn_, map_dy_k_, map_dy_mn_, map_dh_k_, map_dh_mn_;
+  CUtensorMap map_x_k_[2], map_x_mn_[2], map_act_k_[2], map_act_mn_[2], map_dy_k_[2], map_dy_mn_[2], map_dh_k_[2],
+      map_dh_mn_[2];
   std::map<std::tuple<const void*, uint32_t, int64_t, int64_t>, CUtensorMap> weight_maps_;
 
-  cudaStream_t comm_stream_ = nullptr, aux_stream_ = nullptr;
-  cudaEvent_t ev_dw_ = nullptr, ev_dsw_ = nullptr, ev_tgd_ = nullptr, ev_aux_done_ = nullptr;
-  bool bwd_aux_pending_ = false;
+  cudaStream_t comm_stream_ = nullptr, aux_stream_ = nullptr, chain_[2] = {};
+  cudaEvent_t ev_down_[2] = {}, ev_dd_[2] = {}, ev_ds_[2] = {}, ev_dx_[2] = {}, ev_tgd_[2] = {}, ev_tgu_[2] = {};
   cudaEvent_t ev_pass_ = nullptr, ev_put_[4] = {}, ev_done_[4] = {};
   int32_t* host_header_ = nullptr;  // pinned: 16 plan header ints + 8 status ints
 
