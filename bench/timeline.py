@@ -6,6 +6,8 @@ stream) and gaps that a serialising profiler hides.
 
     python bench/timeline.py                 # DeepSeek-V3-size layer, 256 experts on this GPU
     python bench/timeline.py --experts 32    # the per-GPU share of an 8-GPU run (32 experts, same tokens)
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 bench/timeline.py
+                                             # rank 0's timeline inside a real 8-GPU run
 """
 
 import argparse
@@ -33,14 +35,24 @@ def main():
     ap.add_argument("--comm-dtype", default=None)
     ap.add_argument("--quiet", action="store_true", help="only the per-kernel summary")
     args = ap.parse_args()
-    dev = torch.device("cuda:0")
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
     T, D, F, E, K = args.tokens, args.hidden, args.ffn, args.experts, args.top_k
+    L = E // world
     cfg = ChunkedMoEConfig(num_experts=E, top_k=K, slice_size=args.slice_size, transport="nvshmem",
                            expert_compute="fused", stripe_width=64, comm_dtype=args.comm_dtype)
-    gen = torch.Generator(device=dev).manual_seed(0)
-    w_up = torch.empty(E, D, 2 * F, device=dev, dtype=torch.bfloat16)
-    w_down = torch.empty(E, F, D, device=dev, dtype=torch.bfloat16)
-    for l in range(E):
+    gen = torch.Generator(device=dev).manual_seed(rank)
+    w_up = torch.empty(L, D, 2 * F, device=dev, dtype=torch.bfloat16)
+    w_down = torch.empty(L, F, D, device=dev, dtype=torch.bfloat16)
+    for l in range(L):
         w_up[l] = (torch.randn(D, 2 * F, generator=gen, device=dev) * 0.006).to(torch.bfloat16)
         w_down[l] = (torch.randn(F, D, generator=gen, device=dev) * 0.006).to(torch.bfloat16)
     w_up.requires_grad_(True)
@@ -59,9 +71,20 @@ def main():
     for _ in range(3):
         step()
     torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
     with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
         step()
         torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        from chunked_ep_moe_b200.ops import fused
+
+        if rank != 0:
+            fused.release_workspaces()
+            dist.destroy_process_group()
+            return
     events = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
                     key=lambda e: e.time_range.start)
     t0 = events[0].time_range.start
@@ -82,6 +105,11 @@ def main():
         print(f"{key:32s} {n:6d} {total:10.3f} {total / n:10.3f}")
     flops = 24.0 * D * F * T * K
     print(f"\nstep span {span:.3f} ms   {T / (span / 1e3):.0f} tokens/s   {flops / (span / 1e3) / 1e12:.0f} TFLOP/s")
+    if world > 1:
+        from chunked_ep_moe_b200.ops import fused
+
+        fused.release_workspaces()
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
