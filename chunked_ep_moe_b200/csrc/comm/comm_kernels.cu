@@ -111,6 +111,20 @@ __global__ void __launch_bounds__(kPutThreads) dispatch_put_kernel(const PutPara
   const int buf = static_cast<int>(p.seq & 1u);
   const int S = p.lay.S, D = p.hidden;
   const int warps_total = gridDim.x * (kPutThreads / 32);
+  // Arrival releases are batched: a system-scope fence drains this warp's stores over NVLink, so one fence covers
+  // up to kPendingSignals chunks instead of one (lane i of the warp keeps pending signal i).
+  constexpr int kPendingSignals = 8;
+  uint32_t* pend_ptr = nullptr;
+  uint32_t pend_cnt = 0;
+  int pending = 0;
+  auto flush = [&]() {
+    __syncwarp();
+    if (lane < pending) {
+      __threadfence_system();
+      red_add_release_sys(pend_ptr, pend_cnt);
+    }
+    pending = 0;
+  };
   for (int c = blockIdx.x * (kPutThreads / 32) + warp; c < num_chunks; c += warps_total) {
     const int seg = find_segment(put, n_seg, c);
     const int4 e = put[seg];  // {send-order offset, rows, dest row, chunk prefix}
@@ -131,12 +145,13 @@ __global__ void __launch_bounds__(kPutThreads) dispatch_put_kernel(const PutPara
       }
       if (lane == 0) p.peer_w[r][drow] = p.w_flat[flat];
     }
-    __syncwarp();
-    if (lane == 0) {
-      __threadfence_system();
-      red_add_release_sys(p.peer_arrive[r] + p.me * p.lay.L + l, static_cast<uint32_t>(rows));
+    if (lane == pending) {
+      pend_ptr = p.peer_arrive[r] + p.me * p.lay.L + l;
+      pend_cnt = static_cast<uint32_t>(rows);
     }
+    if (++pending == kPendingSignals) flush();
   }
+  flush();
 }
 
 __global__ void slice_done_kernel(uint32_t* const* peer_credit, int num_ranks, int me, uint32_t seq) {

@@ -72,9 +72,11 @@ __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)
 
 // Epilogue of one 128 x 256 accumulator tile. `tacc` is this warp's TMEM address (lane quarter q, accumulator
 // buffer), `tl` the tile as THIS CTA sees it (its 128 rows), `stage_gen` the warp's 8 KB staging buffer.
+// `returned` (combine modes): lane s of every epilogue warp counts the row pieces this warp has stored to source
+// rank s so far; `flush_returned` releases them once, after the CTA's last tile.
 template <int MODE>
 __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl, uint32_t tacc, int q, int lane,
-                                             uint8_t* stage_gen) {
+                                             uint8_t* stage_gen, uint32_t& returned) {
   using Traits = ModeTraits<MODE>;
   const int row = q * 32 + lane;  // tile row owned by this thread
   const int grow = tl.row0 + row;
@@ -311,6 +313,16 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
                           __uint_as_float(r[4 * i + 3]));
       }
     }
+  }
+}
+
+// Releases this warp's returned-row counts to their source ranks: every lane's stores are ordered before the
+// warp barrier, lane s then fences at system scope and adds its count to source s's counter.
+__device__ __forceinline__ void flush_returned(const GemmParams& p, int lane, uint32_t returned) {
+  __syncwarp();
+  if (lane < p.lay.P && returned > 0) {
+    __threadfence_system();
+    red_add_release_sys(p.peer_count[lane], returned);
   }
 }
 

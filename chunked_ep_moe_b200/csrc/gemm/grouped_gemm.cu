@@ -252,7 +252,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
     // ================================ epilogue ==============================================
     const int q = warp & 3;              // TMEM lane quarter this warp may read
     uint8_t* stage_gen = staging_gen + (warp - 2) * 8192;
-    uint32_t tcount = 0;
+    uint32_t tcount = 0, returned = 0;
     for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x, ++tcount) {
       const Tile tl = decode_tile<MODE>(p, t, num_entries);
       const int as = tcount & 1;
@@ -266,12 +266,13 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
       if (!ok) break;
       tcgen05_fence_after_sync();
       const uint32_t tacc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * kBlockN;
-      run_epilogue<MODE>(p, tl, tacc, q, lane, stage_gen);
+      run_epilogue<MODE>(p, tl, tacc, q, lane, stage_gen, returned);
       // Hand the accumulator buffer back to the MMA warp.
       tcgen05_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar(as));
     }
+    if constexpr (Traits::kCombine) flush_returned(p, lane, returned);  // also on the unwind path: what was stored is released
   }
 
   // ================================ teardown ================================================

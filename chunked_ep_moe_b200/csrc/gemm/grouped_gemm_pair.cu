@@ -317,7 +317,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
     const int q = warp & 3;
     uint8_t* stage_gen = staging_gen + (warp - 2) * 8192;
     const uint32_t leader_acc_empty0 = map_to_cta(acc_empty_bar(0), 0);
-    uint32_t tcount = 0;
+    uint32_t tcount = 0, returned = 0;
     for (int t = first_tile; t < num_tiles && !*abort_flag; t += tile_step, ++tcount) {
       const Tile tl = decode_pair_tile<MODE>(p, t, num_entries, rank);
       const int as = tcount & 1;
@@ -331,11 +331,12 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
       if (!ok) break;
       tcgen05_fence_after_sync();
       const uint32_t tacc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * kBlockN;
-      run_epilogue<MODE>(p, tl, tacc, q, lane, stage_gen);
+      run_epilogue<MODE>(p, tl, tacc, q, lane, stage_gen, returned);
       tcgen05_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(leader_acc_empty0 + 8u * as);
     }
+    if constexpr (Traits::kCombine) flush_returned(p, lane, returned);  // also on the unwind path: what was stored is released
   }
 
   // ================================ teardown ================================================
