@@ -280,17 +280,33 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
                                 static_cast<size_t>(tl.m * kBlockM + q * 32) * n_total + tl.n * kBlockN;
 #pragma unroll 1
       for (int half = 0; half < 2; ++half) {
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          load_chunk(half * 128 + c * 32);
+        auto stage_chunk = [&](int c, const uint32_t (&v)[32]) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const int lc = c * 4 + i;
             *reinterpret_cast<int4*>(stage_gen + lane * 256 + ((lc ^ (lane & 15)) << 4)) =
-                make_int4(pack_bf16(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])),
-                          pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
-                          pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])),
-                          pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7])));
+                make_int4(pack_bf16(__uint_as_float(v[8 * i]), __uint_as_float(v[8 * i + 1])),
+                          pack_bf16(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3])),
+                          pack_bf16(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5])),
+                          pack_bf16(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7])));
+          }
+        };
+        if (first && tl.kblocks > 0) {
+          // Common case (the expert lies inside one slice): two TMEM loads per wait.
+          uint32_t r2[32];
+#pragma unroll 1
+          for (int c = 0; c < 4; c += 2) {
+            tmem_ld_32x32(tacc + half * 128 + c * 32, r);
+            tmem_ld_32x32(tacc + half * 128 + (c + 1) * 32, r2);
+            tmem_ld_wait();
+            stage_chunk(c, r);
+            stage_chunk(c + 1, r2);
+          }
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            load_chunk(half * 128 + c * 32);
+            stage_chunk(c, r);
           }
         }
         __syncwarp();

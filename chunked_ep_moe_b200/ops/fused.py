@@ -89,6 +89,14 @@ def release_workspaces() -> None:
     _workspaces.clear()
 
 
+def last_plan_stats(cfg: ChunkedMoEConfig) -> list:
+    """Load statistics of the most recent pass of every cached workspace (rows, slices, padding, remote rows)."""
+    from ..utils.stats import header_stats
+
+    return [header_stats(list(ws.rank.plan_header()), cfg.slice_size) for ws in _workspaces.values()
+            if ws.rank is not None]
+
+
 def launches() -> int:
     """Kernels launched so far by every cached workspace of this process."""
     return sum(int(ws.rank.launches()) for ws in _workspaces.values() if ws.rank is not None)

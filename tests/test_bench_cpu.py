@@ -1,0 +1,50 @@
+"""bench.py pieces that run without a GPU: routing generators, the clock-sample parser, the reference arm's line."""
+
+import json
+import os
+import subprocess
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import bench  # noqa: E402
+
+
+def test_reference_arm_reports_unavailable():
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference"], capture_output=True,
+                         text=True, timeout=120)
+    assert out.returncode == 0
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and "unavailable" in line
+
+
+def test_routing_generators():
+    gen = torch.Generator().manual_seed(0)
+    for skew in ("none", "zipf", "expert0"):
+        ids, w = bench.make_routing(gen, 512, 64, 8, skew, "cpu")
+        assert ids.shape == (512, 8) and ids.dtype == torch.int32 and w.shape == (512, 8)
+        assert int(ids.min()) >= 0 and int(ids.max()) < 64
+        assert torch.allclose(w.sum(-1), torch.ones(512), atol=1e-5)
+        assert all(len(set(row.tolist())) == 8 for row in ids[:32]), "experts of one token must be distinct"
+        if skew == "expert0":
+            assert (ids[:, 0] == 0).all()
+    ids, _ = bench.make_routing(gen, 4096, 64, 8, "zipf", "cpu")
+    counts = torch.bincount(ids.reshape(-1).long(), minlength=64)
+    assert counts[0] > 4 * counts[32:].float().mean(), "Zipf routing must be visibly skewed"
+
+
+def test_clock_sample_parser(tmp_path):
+    sampler = bench.ClockSampler(0)
+    sampler.proc = type("P", (), {"terminate": lambda s: None, "wait": lambda s, timeout=None: 0,
+                                   "kill": lambda s: None})()
+    with open(sampler.path, "w") as f:
+        f.write("0, 1320, 1965, 998.1, 0x0000000000000004, Not Active, Not Active, Not Active, Active\n")
+        f.write("0, 1340, 1965, 1001.7, 0x0000000000000004, Not Active, Not Active, Not Active, Active\n")
+        f.write("0, 1965, 1965, 300.0, 0x0000000000000000, Not Active, Not Active, Not Active, Not Active\n")
+        f.write("garbage line\n")
+    got = sampler.stop()
+    assert got["sm_mhz"] == 1340.0 and got["sm_max_mhz"] == 1965.0
+    assert got["reasons"] == ["sw_power_cap"] and got["samples"] == 3
