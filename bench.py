@@ -184,32 +184,40 @@ def main():
         out.backward(g_d)
         return out, x.grad, weights.grad
 
-    # End-to-end step: this step's inputs come from pinned host memory (copied on a side stream while the previous
-    # step computes, double buffered) and the step's scalar result is read back to the host before the step ends.
+    # End-to-end step: this step's inputs come from pinned host memory (copied on a side stream into one of two
+    # preallocated device slots while the previous step computes) and the step's scalar result is read back to the
+    # host before the step ends.
     copy_stream = torch.cuda.Stream(device=dev)
-    staged = [None, None]
+    slots = [(torch.empty_like(x_d), torch.empty_like(ids_d), torch.empty_like(weights_d)) for _ in range(2)]
+    ready = [torch.cuda.Event(), torch.cuda.Event()]
+    consumed = [None, None]
+    staged = [False, False]
+    e2e_count = [0]
 
     def stage_inputs(slot):
         with torch.cuda.stream(copy_stream):
-            staged[slot] = (x_h.to(dev, non_blocking=True), ids_h.to(dev, non_blocking=True),
-                            weights_h.to(dev, non_blocking=True), torch.cuda.Event())
-            staged[slot][3].record(copy_stream)
-
-    e2e_count = [0]
+            if consumed[slot] is not None:
+                copy_stream.wait_event(consumed[slot])  # the step that last read this slot has finished
+            slots[slot][0].copy_(x_h, non_blocking=True)
+            slots[slot][1].copy_(ids_h, non_blocking=True)
+            slots[slot][2].copy_(weights_h, non_blocking=True)
+            ready[slot].record(copy_stream)
+        staged[slot] = True
 
     def step_e2e():
         slot = e2e_count[0] & 1
-        if staged[slot] is None:
+        if not staged[slot]:
             stage_inputs(slot)
-        x, ids, weights, ready = staged[slot]
-        staged[slot] = None
-        torch.cuda.current_stream().wait_event(ready)
-        for t in (x, ids, weights):
-            t.record_stream(torch.cuda.current_stream())
+        cur = torch.cuda.current_stream()
+        cur.wait_event(ready[slot])
+        staged[slot] = False
         stage_inputs(slot ^ 1)  # the next step's copy overlaps this step's compute
-        out, dx, dw = step(x, ids, weights)
+        x, ids, weights = slots[slot]
+        out, dx, dw = step(x.detach(), ids, weights.detach())
         loss_h.copy_((out.float().mean() + dx.float().mean()).reshape(1), non_blocking=True)
-        torch.cuda.current_stream().synchronize()  # the host owns the step's result before the next step starts
+        consumed[slot] = torch.cuda.Event()
+        consumed[slot].record(cur)
+        cur.synchronize()  # the host owns the step's result before the next step starts
         e2e_count[0] += 1
         return float(loss_h[0])
 

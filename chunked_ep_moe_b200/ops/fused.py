@@ -61,7 +61,8 @@ class FusedWorkspace:
         self.arena = SymmetricArena(nbytes, group, solo=self.world == 1)
         self.rank = ext.FusedRank(
             P=self.world, L=self.local_experts, me=self.rank_index, S=cfg.slice_size, D=hidden, F=ffn, K=cfg.top_k,
-            stripe=cfg.stripe_width, tk_cap=tk_cap, max_slices=self.max_slices, num_sms=cfg.num_sms, fp8=self.fp8,
+            stripe=cfg.stripe_width, tk_cap=tk_cap, max_slices=self.max_slices,
+            num_sms=int(os.environ.get("CEM_GEMM_GRID", cfg.num_sms)), fp8=self.fp8,
             arena=self.arena.local, peer_arenas=self.arena.peers, use_comm_stream=True,
             spin_limit=_DEFAULT_SPIN_LIMIT, put_blocks=int(os.environ.get("CEM_PUT_BLOCKS", _PUT_BLOCKS)),
             cta_pairs=os.environ.get("CEM_CTA_PAIRS", "0") != "0")
