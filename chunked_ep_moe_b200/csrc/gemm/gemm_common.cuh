@@ -70,13 +70,16 @@ __device__ __forceinline__ void resolve_source(const GemmParams& p, int g, int g
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
 
+// `col0`, `ncols` (weight-gradient mode only): the accumulator columns this warp is responsible for; that mode may
+// run two epilogue warps per TMEM lane quarter, each taking half of the columns.
 // Epilogue of one 128 x 256 accumulator tile. `tacc` is this warp's TMEM address (lane quarter q, accumulator
 // buffer), `tl` the tile as THIS CTA sees it (its 128 rows), `stage_gen` the warp's 8 KB staging buffer.
 // `returned` (combine modes): lane s of every epilogue warp counts the row pieces this warp has stored to source
 // rank s so far; `flush_returned` releases them once, after the CTA's last tile.
 template <int MODE>
 __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl, uint32_t tacc, int q, int lane,
-                                             uint8_t* stage_gen, uint32_t& returned) {
+                                             uint8_t* stage_gen, uint32_t& returned, int col0 = 0,
+                                             int ncols = kBlockN) {
   using Traits = ModeTraits<MODE>;
   const int row = q * 32 + lane;  // tile row owned by this thread
   const int grow = tl.row0 + row;
@@ -274,57 +277,54 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
       }
     };
     if (final) {
-      // bf16 gradient: transpose through the warp's staging buffer so every store instruction
-      // writes two full 256-byte row pieces instead of 32 scattered 16-byte ones.
+      // bf16 gradient: transpose 64-column passes through the warp's staging buffer (32 rows x 128 bytes, 16-byte
+      // chunks XOR-swizzled by row) so every store instruction writes four full 128-byte row pieces instead of 32
+      // scattered 16-byte ones.
       __nv_bfloat16* warp_out = p.grad_out + static_cast<size_t>(tl.g) * m_total * n_total +
                                 static_cast<size_t>(tl.m * kBlockM + q * 32) * n_total + tl.n * kBlockN;
-#pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
-        auto stage_chunk = [&](int c, const uint32_t (&v)[32]) {
+      auto stage_chunk = [&](int c, const uint32_t (&v)[32]) {  // c: 32-column chunk inside the pass (0 or 1)
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int lc = c * 4 + i;
-            *reinterpret_cast<int4*>(stage_gen + lane * 256 + ((lc ^ (lane & 15)) << 4)) =
-                make_int4(pack_bf16(__uint_as_float(v[8 * i]), __uint_as_float(v[8 * i + 1])),
-                          pack_bf16(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3])),
-                          pack_bf16(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5])),
-                          pack_bf16(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7])));
-          }
-        };
+        for (int i = 0; i < 4; ++i) {
+          const int lc = c * 4 + i;
+          *reinterpret_cast<int4*>(stage_gen + lane * 128 + ((lc ^ (lane & 7)) << 4)) =
+              make_int4(pack_bf16(__uint_as_float(v[8 * i]), __uint_as_float(v[8 * i + 1])),
+                        pack_bf16(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3])),
+                        pack_bf16(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5])),
+                        pack_bf16(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7])));
+        }
+      };
+#pragma unroll 1
+      for (int col = col0; col < col0 + ncols; col += 64) {
         if (first && tl.kblocks > 0) {
           // Common case (the expert lies inside one slice): two TMEM loads per wait.
           uint32_t r2[32];
-#pragma unroll 1
-          for (int c = 0; c < 4; c += 2) {
-            tmem_ld_32x32(tacc + half * 128 + c * 32, r);
-            tmem_ld_32x32(tacc + half * 128 + (c + 1) * 32, r2);
-            tmem_ld_wait();
-            stage_chunk(c, r);
-            stage_chunk(c + 1, r2);
-          }
+          tmem_ld_32x32(tacc + col, r);
+          tmem_ld_32x32(tacc + col + 32, r2);
+          tmem_ld_wait();
+          stage_chunk(0, r);
+          stage_chunk(1, r2);
         } else {
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            load_chunk(half * 128 + c * 32);
-            stage_chunk(c, r);
-          }
+          load_chunk(col);
+          stage_chunk(0, r);
+          load_chunk(col + 32);
+          stage_chunk(1, r);
         }
         __syncwarp();
-#pragma unroll 4
-        for (int rr = 0; rr < 16; ++rr) {
-          const int rsel = rr * 2 + (lane >> 4), c16 = lane & 15;
-          const int4 v = *reinterpret_cast<const int4*>(stage_gen + rsel * 256 + ((c16 ^ (rsel & 15)) << 4));
-          *reinterpret_cast<int4*>(warp_out + static_cast<size_t>(rsel) * n_total + half * 128 + c16 * 8) = v;
+#pragma unroll
+        for (int rr = 0; rr < 8; ++rr) {
+          const int rsel = rr * 4 + (lane >> 3), c8 = lane & 7;
+          const int4 v = *reinterpret_cast<const int4*>(stage_gen + rsel * 128 + ((c8 ^ (rsel & 7)) << 4));
+          *reinterpret_cast<int4*>(warp_out + static_cast<size_t>(rsel) * n_total + col + c8 * 8) = v;
         }
         __syncwarp();
       }
     } else {
 #pragma unroll 1
-      for (int c = 0; c < 8; ++c) {
-        load_chunk(c * 32);
+      for (int col = col0; col < col0 + ncols; col += 32) {
+        load_chunk(col);
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-          *reinterpret_cast<float4*>(cout + c * 32 + 4 * i) =
+          *reinterpret_cast<float4*>(cout + col + 4 * i) =
               make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]),
                           __uint_as_float(r[4 * i + 3]));
       }

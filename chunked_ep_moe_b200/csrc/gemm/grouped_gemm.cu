@@ -51,8 +51,14 @@ __device__ __forceinline__ void issue_kblock(const GemmParams& p, const Tile& tl
   }
 }
 
+// The weight-gradient mode runs EIGHT epilogue warps (two per TMEM lane quarter, each taking 128 of the 256
+// accumulator columns): with few rows per expert its tiles have 4-5 k-blocks and 64 KB of output, so the epilogue,
+// not the mainloop, sets the pace.
 template <int MODE>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+constexpr int epilogue_warps() { return MODE == kModeTgmm ? 8 : 4; }
+
+template <int MODE>
+__global__ void __launch_bounds__(64 + 32 * epilogue_warps<MODE>(), 1)
 grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_b) {
   using Traits = ModeTraits<MODE>;
@@ -89,7 +95,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(acc_full_bar(s), 1);
-      mbar_init(acc_empty_bar(s), 4);
+      mbar_init(acc_empty_bar(s), epilogue_warps<MODE>());
     }
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
@@ -251,7 +257,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
   } else {
     // ================================ epilogue ==============================================
     const int q = warp & 3;              // TMEM lane quarter this warp may read
-    uint8_t* stage_gen = staging_gen + (warp - 2) * 8192;
+    const int ew = warp - 2;             // epilogue warp index
+    const int col0 = (MODE == kModeTgmm) ? (ew >> 2) * (kBlockN / 2) : 0;
+    const int ncols = (MODE == kModeTgmm) ? kBlockN / 2 : kBlockN;
+    uint8_t* stage_gen = staging_gen + ew * (kStagingBytes / epilogue_warps<MODE>());
     uint32_t tcount = 0, returned = 0;
     for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x, ++tcount) {
       const Tile tl = decode_tile<MODE>(p, t, num_entries);
@@ -266,7 +275,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
       if (!ok) break;
       tcgen05_fence_after_sync();
       const uint32_t tacc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * kBlockN;
-      run_epilogue<MODE>(p, tl, tacc, q, lane, stage_gen, returned);
+      run_epilogue<MODE>(p, tl, tacc, q, lane, stage_gen, returned, col0, ncols);
       // Hand the accumulator buffer back to the MMA warp.
       tcgen05_fence_before_sync();
       __syncwarp();
@@ -295,7 +304,7 @@ void launch_grouped_gemm(int mode, const GemmParams& p, const CUtensorMap& map_a
       cudaFuncSetAttribute(grouped_gemm_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes); \
       configured = true;                                                                                      \
     }                                                                                                         \
-    grouped_gemm_kernel<M><<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(p, map_a, map_b);                  \
+    grouped_gemm_kernel<M><<<grid, 64 + 32 * epilogue_warps<M>(), kGemmSmemBytes, stream>>>(p, map_a, map_b);                  \
     break;                                                                                                    \
   }
   switch (mode) {
