@@ -51,11 +51,11 @@ __device__ __forceinline__ void issue_kblock(const GemmParams& p, const Tile& tl
   }
 }
 
-// The weight-gradient mode runs EIGHT epilogue warps (two per TMEM lane quarter, each taking 128 of the 256
-// accumulator columns): with few rows per expert its tiles have 4-5 k-blocks and 64 KB of output, so the epilogue,
-// not the mainloop, sets the pace.
+// Epilogue warps per CTA. Two warps per TMEM lane quarter (8 in all, each taking 128 of the 256 accumulator columns)
+// were measured for the weight-gradient mode and changed nothing (0.659 vs 0.636 ms per launch at 256 experts per GPU):
+// with ~256 rows per expert that mode is bound by the 22.5 GB of gradients it writes per pass, not by its epilogue.
 template <int MODE>
-constexpr int epilogue_warps() { return MODE == kModeTgmm ? 8 : 4; }
+constexpr int epilogue_warps() { return 4; }
 
 template <int MODE>
 __global__ void __launch_bounds__(64 + 32 * epilogue_warps<MODE>(), 1)
