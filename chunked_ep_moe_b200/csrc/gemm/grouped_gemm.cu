@@ -258,8 +258,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
     // ================================ epilogue ==============================================
     const int q = warp & 3;              // TMEM lane quarter this warp may read
     const int ew = warp - 2;             // epilogue warp index
-    const int col0 = (MODE == kModeTgmm) ? (ew >> 2) * (kBlockN / 2) : 0;
-    const int ncols = (MODE == kModeTgmm) ? kBlockN / 2 : kBlockN;
+    constexpr int kColsPerWarp = kBlockN * 4 / epilogue_warps<MODE>();  // warps sharing a lane quarter split the columns
+    const int col0 = (ew >> 2) * kColsPerWarp;
+    const int ncols = kColsPerWarp;
     uint8_t* stage_gen = staging_gen + ew * (kStagingBytes / epilogue_warps<MODE>());
     uint32_t tcount = 0, returned = 0;
     for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x, ++tcount) {
