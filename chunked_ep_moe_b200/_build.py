@@ -8,6 +8,7 @@ machine; loading the module needs no GPU either (the CPU plan builder lives in i
 
 from __future__ import annotations
 
+import hashlib
 import importlib.util
 import os
 import sys
@@ -44,16 +45,30 @@ def _so_path() -> str:
     return os.path.join(_BUILD_DIR, _NAME + ".so")
 
 
+def _source_digest() -> str:
+    """Content hash of every file under csrc/ (what the built object depends on)."""
+    h = hashlib.sha256()
+    for root, dirs, files in os.walk(_CSRC):
+        dirs.sort()
+        for f in sorted(files):
+            path = os.path.join(root, f)
+            h.update(os.path.relpath(path, _CSRC).encode())
+            with open(path, "rb") as fh:
+                h.update(fh.read())
+    return h.hexdigest()
+
+
+def _digest_path() -> str:
+    return os.path.join(_BUILD_DIR, _NAME + ".sha256")
+
+
 def _is_stale() -> bool:
-    so = _so_path()
-    if not os.path.exists(so):
+    """True when there is no built object or it was built from different sources (file times play no role:
+    a copied tree keeps its object usable)."""
+    if not os.path.exists(_so_path()) or not os.path.exists(_digest_path()):
         return True
-    built = os.path.getmtime(so)
-    for root, _, files in os.walk(_CSRC):
-        for f in files:
-            if os.path.getmtime(os.path.join(root, f)) > built:
-                return True
-    return False
+    with open(_digest_path()) as f:
+        return f.read().strip() != _source_digest()
 
 
 def build(verbose: bool = False, force: bool = False):
@@ -80,6 +95,8 @@ def build(verbose: bool = False, force: bool = False):
                 verbose=verbose,
                 is_python_module=False,
             )
+            with open(_digest_path(), "w") as f:
+                f.write(_source_digest())
         spec = importlib.util.spec_from_file_location(_NAME, _so_path())
         module = importlib.util.module_from_spec(spec)
         import torch  # noqa: F401  (libtorch must be loaded before the extension)
