@@ -107,6 +107,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("plan_header", &cem::FusedRank::plan_header)
       .def("plan_ints", &cem::FusedRank::plan_ints)
       .def("launches", &cem::FusedRank::launches)
+      .def("set_pipeline_counters", &cem::FusedRank::set_pipeline_counters, py::arg("counters") = py::none())
       .def("act", &cem::FusedRank::act)
       .def("h", &cem::FusedRank::h)
       .def("dh", &cem::FusedRank::dh)

@@ -169,14 +169,11 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
         p.peer_dw[src][pos] = dw;
       }
     }
-    // One release per (warp, source): tells the source how many row pieces just landed.
-    __syncwarp();
+    // Lane s keeps the count of row pieces this warp has stored to source rank s; nothing is released here, so the
+    // stores of consecutive tiles stay in flight together (`flush_returned` releases once, after the last tile).
     for (int s = 0; s < p.lay.P; ++s) {
       const uint32_t cnt = __popc(__ballot_sync(0xffffffffu, src == s));
-      if (lane == s && cnt > 0) {
-        __threadfence_system();
-        red_add_release_sys(p.peer_count[s], cnt);
-      }
+      if (lane == s) returned += cnt;
     }
   } else if constexpr (MODE == kModeDownDw) {
     const float w = valid ? p.row_w[grow] : 0.0f;

@@ -81,6 +81,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(staging_gen + kStagingBytes + 8 * (2 * kStages + 5) + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool counting = p.prof != nullptr;
+  auto prof_add = [&](int slot, long long v) {
+    atomicAdd(p.prof + static_cast<size_t>(blockIdx.x) * kProfSlots + slot, static_cast<unsigned long long>(v));
+  };
 
   // An earlier kernel of this pass already gave up: do nothing, so the error reaches the host quickly.
   __shared__ int s_early;
@@ -120,6 +124,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
     // ================================ TMA producer ==========================================
     uint32_t it = 0;
     int waited_expert = -1;
+    long long empty_wait = 0;
     for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
       const Tile tl = decode_tile<MODE>(p, t, num_entries);
       if constexpr (MODE == kModeSwiglu) {
@@ -148,11 +153,13 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
         for (int kb = 0; kb < tl.kblocks; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
+          const long long w0 = counting ? clock64() : 0;
           if (!mbar_wait(empty_bar(s), ph ^ 1u, p.mbar_limit)) {
             report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 100 + s, 0, 0);
             *abort_flag = 1;
             break;
           }
+          if (counting) empty_wait += clock64() - w0;
           const uint32_t sa = smem_base + s * kStageBytes;
           const uint32_t sb = sa + kStageBytesA;
           mbar_expect_tx(full_bar(s), kStageBytes);
@@ -161,6 +168,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
       }
       __syncwarp();
     }
+    if (counting && lane == 0) prof_add(kProfEmptyWait, empty_wait);
     if (lane == 0 && *abort_flag) {
       // Unwinding: let our copies in flight land before the CTA gives its shared memory back.
       for (int s = 0; s < kStages; ++s) {
@@ -172,74 +180,100 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
     }
   } else if (warp == 1) {
     // ================================ MMA issuer ============================================
+    // ONE thread walks the k-blocks on its own: wait, fence, four MMAs, commit. Nothing in that loop involves the
+    // other lanes (a warp-wide vote and barrier per k-block cost ~400 of ~800 cycles per k-block and left the
+    // tensor pipe idle a third of the time); the warp only meets once per tile, and for the one weight-gradient
+    // k-block per tile whose rows past the group end must be zeroed by all lanes.
     constexpr uint32_t idesc = make_instr_desc_bf16(kBlockM, kBlockN, Traits::kAMn, Traits::kBMn);
+    constexpr uint32_t kDescStepA = Traits::kAMn ? 2048u : 32u;  // bytes per 16-wide k step inside a stage
+    constexpr uint32_t kDescStepB = Traits::kBMn ? 2048u : 32u;
     uint32_t it = 0, tcount = 0;
+    long long full_wait = 0, acc_wait = 0;
+    const long long loop_c0 = counting ? clock64() : 0;
+    const uint64_t loop_n0 = counting ? global_timer_ns() : 0;
+    // Issues `ksteps` MMAs of pipeline iteration `i` (lane 0 only) and frees the stage behind them.
+    auto issue_stage = [&](uint32_t i, uint32_t tmem_d, int ksteps, bool first_kblock) {
+      const uint32_t sa = smem_base + (i % kStages) * kStageBytes;
+      const uint64_t da = Traits::kAMn ? make_smem_desc(sa, 8192, 1024) : make_smem_desc(sa, 16, 1024);
+      const uint64_t db = Traits::kBMn ? make_smem_desc(sa + kStageBytesA, 8192, 1024)
+                                       : make_smem_desc(sa + kStageBytesA, 16, 1024);
+#pragma unroll
+      for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+        // The start address sits in the low 14 bits (16-byte units) and never carries out of them.
+        if (k < ksteps)
+          umma_bf16(tmem_d, da + ((k * kDescStepA) >> 4), db + ((k * kDescStepB) >> 4), idesc,
+                    (!first_kblock || k > 0) ? 1u : 0u);
+      }
+      umma_commit(empty_bar(i % kStages));
+    };
     for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x, ++tcount) {
       const Tile tl = decode_tile<MODE>(p, t, num_entries);
       const int as = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1u;
-      bool ok = true;
+      const uint32_t tmem_d = tmem_base + as * kBlockN;
+      // Weight gradients: the last k-block of a group may hold rows of the next group.
+      const bool ragged_tail = (MODE == kModeTgmm) && (tl.nrows % kBlockK) != 0;
+      const int solo_kblocks = ragged_tail ? tl.kblocks - 1 : tl.kblocks;
       if (lane == 0) {
-        ok = mbar_wait(acc_empty_bar(as), aph ^ 1u, p.mbar_limit);
+        const long long w0 = counting ? clock64() : 0;
+        bool ok = mbar_wait(acc_empty_bar(as), aph ^ 1u, p.mbar_limit);
+        if (counting) acc_wait += clock64() - w0;
         if (!ok) {
           report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 200 + as, 0, 0);
           *abort_flag = 1;
         }
-      }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
-      tcgen05_fence_after_sync();
-      const uint32_t tmem_d = tmem_base + as * kBlockN;
-      for (int kb = 0; kb < tl.kblocks; ++kb, ++it) {
-        const int s = it % kStages;
-        const uint32_t ph = (it / kStages) & 1u;
-        if (lane == 0) {
-          ok = mbar_wait(full_bar(s), ph, p.mbar_limit);
-          if (!ok) {
-            report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 300 + s, 0, 0);
-            *abort_flag = 1;
-          }
-        }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        const uint32_t sa = smem_base + s * kStageBytes;
-        const uint32_t sb = sa + kStageBytesA;
-        int ksteps = kBlockK / kUmmaK;
-        if constexpr (MODE == kModeTgmm) {
-          const int valid = tl.nrows - kb * kBlockK;  // rows of this k-block inside the group
-          if (valid < kBlockK) {
-            ksteps = (valid + kUmmaK - 1) / kUmmaK;
-            // Rows [valid, ksteps*16) belong to the next group (or are padding): zero them in
-            // both operands. Each k row is one 128-byte line per 64-column chunk.
-            uint8_t* ga = smem_gen + s * kStageBytes;
-            const int zrows = ksteps * kUmmaK - valid;
-            for (int idx = lane; idx < zrows * 6 * 8; idx += 32) {
-              const int v16 = idx & 7, line = idx >> 3;
-              const int chunk = line % 6, r = valid + line / 6;
-              *reinterpret_cast<int4*>(ga + chunk * 8192 + r * 128 + v16 * 16) = make_int4(0, 0, 0, 0);
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-          }
-        }
         tcgen05_fence_after_sync();
-        if (lane == 0) {
-#pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            if (k < ksteps) {
-              // K-major: 16 bf16 = 32 bytes along the swizzled row. MN-major: 16 k rows = 2048 bytes.
-              const uint64_t da = Traits::kAMn ? make_smem_desc(sa + k * 2048, 8192, 1024)
-                                               : make_smem_desc(sa + k * 32, 16, 1024);
-              const uint64_t db = Traits::kBMn ? make_smem_desc(sb + k * 2048, 8192, 1024)
-                                               : make_smem_desc(sb + k * 32, 16, 1024);
-              umma_bf16(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        for (int kb = 0; ok && kb < solo_kblocks; ++kb) {
+          const uint32_t i = it + kb;
+          const long long w1 = counting ? clock64() : 0;
+          ok = mbar_wait(full_bar(i % kStages), (i / kStages) & 1u, p.mbar_limit);
+          if (counting) full_wait += clock64() - w1;
+          if (!ok) {
+            report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 300 + (i % kStages), 0, 0);
+            *abort_flag = 1;
+            break;
+          }
+          tcgen05_fence_after_sync();
+          issue_stage(i, tmem_d, kBlockK / kUmmaK, kb == 0);
+        }
+      }
+      __syncwarp();
+      if (*abort_flag) break;
+      it += solo_kblocks;
+      if constexpr (MODE == kModeTgmm) {
+        if (ragged_tail) {
+          const int kb = tl.kblocks - 1;
+          const int s = it % kStages;
+          bool ok = true;
+          if (lane == 0) {
+            const long long w1 = counting ? clock64() : 0;
+            ok = mbar_wait(full_bar(s), (it / kStages) & 1u, p.mbar_limit);
+            if (counting) full_wait += clock64() - w1;
+            if (!ok) {
+              report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 300 + s, 0, 0);
+              *abort_flag = 1;
             }
           }
-          umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) break;
+          const int valid = tl.nrows - kb * kBlockK;  // rows of this k-block inside the group
+          const int ksteps = (valid + kUmmaK - 1) / kUmmaK;
+          // Rows [valid, ksteps*16) belong to the next group (or are padding): zero them in both operands.
+          // Each k row is one 128-byte line per 64-column chunk.
+          uint8_t* ga = smem_gen + s * kStageBytes;
+          const int zrows = ksteps * kUmmaK - valid;
+          for (int idx = lane; idx < zrows * 6 * 8; idx += 32) {
+            const int v16 = idx & 7, line = idx >> 3;
+            const int chunk = line % 6, r = valid + line / 6;
+            *reinterpret_cast<int4*>(ga + chunk * 8192 + r * 128 + v16 * 16) = make_int4(0, 0, 0, 0);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          tcgen05_fence_after_sync();
+          if (lane == 0) issue_stage(it, tmem_d, ksteps, kb == 0);
+          ++it;
         }
-        __syncwarp();
       }
-      if (!ok) break;
       if (lane == 0) {
         if (tl.kblocks > 0) {
           umma_commit(acc_full_bar(as));
@@ -248,6 +282,14 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
         }
       }
       __syncwarp();
+    }
+    if (counting && lane == 0) {
+      prof_add(kProfLoopCycles, clock64() - loop_c0);
+      prof_add(kProfLoopNs, static_cast<long long>(global_timer_ns() - loop_n0));
+      prof_add(kProfFullWait, full_wait);
+      prof_add(kProfAccWait, acc_wait);
+      prof_add(kProfKBlocks, it);
+      prof_add(kProfTiles, tcount);
     }
     if (lane == 0 && *abort_flag) {
       // Unwinding: let the MMAs already issued finish before TMEM is freed.
@@ -263,11 +305,14 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
     const int ncols = kColsPerWarp;
     uint8_t* stage_gen = staging_gen + ew * (kStagingBytes / epilogue_warps<MODE>());
     uint32_t tcount = 0, returned = 0;
+    long long epi_wait = 0;
     for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x, ++tcount) {
       const Tile tl = decode_tile<MODE>(p, t, num_entries);
       const int as = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1u;
+      const long long w0 = counting ? clock64() : 0;
       bool ok = mbar_wait(acc_full_bar(as), aph, p.mbar_limit);
+      if (counting) epi_wait += clock64() - w0;
       if (!ok) {
         report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 400 + as, 0, 0);
         *abort_flag = 1;
@@ -282,6 +327,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar(as));
     }
+    if (counting && ew == 0 && lane == 0) prof_add(kProfEpiWait, epi_wait);
     if constexpr (Traits::kCombine) flush_returned(p, lane, returned);  // also on the unwind path: what was stored is released
   }
 

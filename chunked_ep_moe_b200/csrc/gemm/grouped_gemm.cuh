@@ -29,6 +29,19 @@ enum GemmMode : int {
   kModeTgmm = 5,     // dW[g] = lhs[rows_g]^T rhs[rows_g], fp32 carry across slices         (tgmm + accumulate)
 };
 
+// Per-CTA pipeline counters (SM cycles unless noted). They say which side of the operand ring waits for the other.
+enum ProfSlot : int {
+  kProfLoopCycles = 0,   // MMA warp: first tile started -> last MMA issued
+  kProfLoopNs = 1,       // the same span in nanoseconds of the global timer (cycles / ns = SM clock in GHz)
+  kProfEmptyWait = 2,    // producer: waiting for a free stage (the MMAs are the slower side)
+  kProfFullWait = 3,     // MMA warp: waiting for a filled stage (the loads are the slower side)
+  kProfAccWait = 4,      // MMA warp: waiting for the epilogue to hand an accumulator back
+  kProfKBlocks = 5,      // k-blocks issued
+  kProfEpiWait = 6,      // first epilogue warp: waiting for a finished accumulator
+  kProfTiles = 7,        // tiles
+  kProfSlots = 8,
+};
+
 struct GemmParams {
   // --- schedule ---------------------------------------------------------------------------
   const int* plan;   // per-pass plan buffer (see plan_tables.cuh)
@@ -43,6 +56,8 @@ struct GemmParams {
   uint32_t spin_limit;   // polls of a cross-GPU flag before giving up
   uint32_t mbar_limit;   // microseconds a pipeline barrier may take before giving up
   StatusBlock* status;
+  // Optional pipeline counters of this mode, [grid][kProfSlots] summed over launches; null = not counted.
+  unsigned long long* prof;
   // --- arrival flags (swiglu consumer) -----------------------------------------------------
   const uint32_t* arrive;     // [P*L] cumulative rows received per (source, local expert); null = no wait
   const uint32_t* pass_base;  // [P*L] value of `arrive` when this pass began

@@ -115,6 +115,10 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = static_cast<int>(cluster_cta_rank());
   const bool leader = rank == 0;
+  const bool counting = p.prof != nullptr;
+  auto prof_add = [&](int slot, long long v) {
+    atomicAdd(p.prof + static_cast<size_t>(blockIdx.x) * kProfSlots + slot, static_cast<unsigned long long>(v));
+  };
 
   // An earlier kernel of this pass already gave up: both CTAs of the pair leave together (the leader decides).
   __shared__ int s_early;
@@ -161,6 +165,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
     // ================================ TMA producer (both CTAs) ==============================
     uint32_t it = 0;
     int waited_expert = -1;
+    long long empty_wait = 0;
     for (int t = first_tile; t < num_tiles && !*abort_flag; t += tile_step) {
       const Tile tl = decode_pair_tile<MODE>(p, t, num_entries, rank);
       if constexpr (MODE == kModeSwiglu) {
@@ -188,11 +193,13 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
         for (int kb = 0; kb < tl.kblocks; ++kb, ++it) {
           const int s = it % kPairStages;
           const uint32_t ph = (it / kPairStages) & 1u;
+          const long long w0 = counting ? clock64() : 0;
           if (!mbar_wait_poll(empty_bar(s), ph ^ 1u, p.mbar_limit)) {
             report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1100 + s, 0, 0);
             *abort_flag = 1;
             break;
           }
+          if (counting) empty_wait += clock64() - w0;
           const uint32_t sa = smem_base + s * kPairStageBytes;
           const uint32_t fb = kRelay ? full_bar(s) : map_to_cta(full_bar(s), 0);
           if (kRelay) mbar_expect_tx(fb, kPairStageBytes); else mbar_expect_tx_cluster(fb, kPairStageBytes);
@@ -201,6 +208,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
       }
       __syncwarp();
     }
+    if (counting && lane == 0) prof_add(kProfEmptyWait, empty_wait);
     if (lane == 0 && *abort_flag && (kRelay || leader)) {
       for (int s = 0; s < kPairStages; ++s) {
         if (it > static_cast<uint32_t>(s)) {
@@ -211,92 +219,120 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
     }
   } else if (warp == 1) {
     // ================================ MMA issuer (leader) / stage relay (peer) ==============
+    // As in the single-CTA kernel, ONE thread walks the k-blocks on its own; the warp meets once per tile and for
+    // the one weight-gradient k-block per tile whose rows past the group end are zeroed by all lanes.
     constexpr uint32_t idesc = make_instr_desc_bf16(2 * kBlockM, kBlockN, Traits::kAMn, Traits::kBMn);
+    constexpr uint32_t kDescStepA = Traits::kAMn ? 2048u : 32u;
+    constexpr uint32_t kDescStepB = Traits::kBMn ? 2048u : 32u;
     const uint32_t peer = static_cast<uint32_t>(rank ^ 1);
     uint32_t it = 0, tcount = 0;
+    long long full_wait = 0, acc_wait = 0;
+    const long long loop_c0 = counting ? clock64() : 0;
+    const uint64_t loop_n0 = counting ? global_timer_ns() : 0;
+    // Leader, lane 0: the pair MMAs of pipeline iteration `i`, then the stage is free in BOTH CTAs.
+    auto issue_stage = [&](uint32_t i, uint32_t tmem_d, int ksteps, bool first_kblock) {
+      const int s = i % kPairStages;
+      const uint32_t sa = smem_base + s * kPairStageBytes;
+      const uint64_t da = Traits::kAMn ? make_smem_desc(sa, 8192, 1024) : make_smem_desc(sa, 16, 1024);
+      const uint64_t db = Traits::kBMn ? make_smem_desc(sa + kPairStageBytesA, 8192, 1024)
+                                       : make_smem_desc(sa + kPairStageBytesA, 16, 1024);
+#pragma unroll
+      for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+        if (k < ksteps)
+          umma_bf16_pair(tmem_d, da + ((k * kDescStepA) >> 4), db + ((k * kDescStepB) >> 4), idesc,
+                         (!first_kblock || k > 0) ? 1u : 0u);
+      }
+      umma_commit_pair(empty_bar(s));
+      umma_commit_pair(map_to_cta(empty_bar(s), peer));
+    };
     for (int t = first_tile; t < num_tiles && !*abort_flag && (kRelay || leader); t += tile_step, ++tcount) {
       const Tile tl = decode_pair_tile<MODE>(p, t, num_entries, rank);
       const int as = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1u;
-      bool ok = true;
-      if (leader) {
-        if (lane == 0) {
+      const uint32_t tmem_d = tmem_base + as * kBlockN;
+      const bool ragged_tail = kRelay && (tl.nrows % kBlockK) != 0;
+      const int solo_kblocks = ragged_tail ? tl.kblocks - 1 : tl.kblocks;
+      if (lane == 0) {
+        bool ok = true;
+        if (leader) {
+          const long long w0 = counting ? clock64() : 0;
           ok = mbar_wait_poll(acc_empty_bar(as), aph ^ 1u, p.mbar_limit);
+          if (counting) acc_wait += clock64() - w0;
           if (!ok) {
             report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1200 + as, 0, 0);
             *abort_flag = 1;
           }
+          tcgen05_fence_after_sync();
         }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        tcgen05_fence_after_sync();
-      }
-      const uint32_t tmem_d = tmem_base + as * kBlockN;
-      for (int kb = 0; kb < tl.kblocks; ++kb, ++it) {
-        const int s = it % kPairStages;
-        const uint32_t ph = (it / kPairStages) & 1u;
-        if (lane == 0) {
+        for (int kb = 0; ok && kb < solo_kblocks; ++kb) {
+          const uint32_t i = it + kb;
+          const int s = i % kPairStages;
+          const uint32_t ph = (i / kPairStages) & 1u;
+          const long long w1 = counting ? clock64() : 0;
           ok = mbar_wait(full_bar(s), ph, p.mbar_limit);
+          if (ok && kRelay && leader) ok = mbar_wait_poll(ready_bar(s), ph, p.mbar_limit);
+          if (counting) full_wait += clock64() - w1;
           if (!ok) {
             report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1300 + s, 0, 0);
             *abort_flag = 1;
+            break;
           }
-        }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        const uint32_t sa = smem_base + s * kPairStageBytes;
-        const uint32_t sb = sa + kPairStageBytesA;
-        int ksteps = kBlockK / kUmmaK;
-        if constexpr (MODE == kModeTgmm) {
-          const int valid = tl.nrows - kb * kBlockK;
-          if (valid < kBlockK) {
-            ksteps = (valid + kUmmaK - 1) / kUmmaK;
-            // Zero this CTA's rows [valid, ksteps*16) in its four 64-column chunks (2 of A, 2 of B).
-            uint8_t* ga = smem_gen + s * kPairStageBytes;
-            const int zrows = ksteps * kUmmaK - valid;
-            for (int idx = lane; idx < zrows * 4 * 8; idx += 32) {
-              const int v16 = idx & 7, line = idx >> 3;
-              const int chunk = line & 3, r = valid + (line >> 2);
-              *reinterpret_cast<int4*>(ga + chunk * 8192 + r * 128 + v16 * 16) = make_int4(0, 0, 0, 0);
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
+          if (!leader) {
+            mbar_arrive_cluster(map_to_cta(ready_bar(s), peer));  // this CTA's half of the stage is in place
+            continue;
           }
+          tcgen05_fence_after_sync();
+          issue_stage(i, tmem_d, kBlockK / kUmmaK, kb == 0);
         }
-        if (!leader) {
-          // This CTA's half of the stage is in place: tell the leader.
-          if (lane == 0) mbar_arrive_cluster(map_to_cta(ready_bar(s), peer));
-          __syncwarp();
-          continue;
-        }
-        if (lane == 0 && kRelay) {
-          ok = mbar_wait_poll(ready_bar(s), ph, p.mbar_limit);
-          if (!ok) {
-            report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1400 + s, 0, 0);
-            *abort_flag = 1;
-          }
-        }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        tcgen05_fence_after_sync();
-        if (lane == 0) {
-#pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            if (k < ksteps) {
-              const uint64_t da = Traits::kAMn ? make_smem_desc(sa + k * 2048, 8192, 1024)
-                                               : make_smem_desc(sa + k * 32, 16, 1024);
-              const uint64_t db = Traits::kBMn ? make_smem_desc(sb + k * 2048, 8192, 1024)
-                                               : make_smem_desc(sb + k * 32, 16, 1024);
-              umma_bf16_pair(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-            }
-          }
-          // The stage is free in BOTH CTAs once these MMAs have read it.
-          umma_commit_pair(empty_bar(s));
-          umma_commit_pair(map_to_cta(empty_bar(s), peer));
-        }
-        __syncwarp();
       }
-      if (!ok) break;
+      __syncwarp();
+      if (*abort_flag) break;
+      it += solo_kblocks;
+      if constexpr (kRelay) {
+        if (ragged_tail) {
+          const int kb = tl.kblocks - 1;
+          const int s = it % kPairStages;
+          const uint32_t ph = (it / kPairStages) & 1u;
+          bool ok = true;
+          if (lane == 0) {
+            ok = mbar_wait(full_bar(s), ph, p.mbar_limit);
+            if (!ok) {
+              report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1300 + s, 0, 0);
+              *abort_flag = 1;
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) break;
+          const int valid = tl.nrows - kb * kBlockK;
+          const int ksteps = (valid + kUmmaK - 1) / kUmmaK;
+          // Zero this CTA's rows [valid, ksteps*16) in its four 64-column chunks (2 of A, 2 of B).
+          uint8_t* ga = smem_gen + s * kPairStageBytes;
+          const int zrows = ksteps * kUmmaK - valid;
+          for (int idx = lane; idx < zrows * 4 * 8; idx += 32) {
+            const int v16 = idx & 7, line = idx >> 3;
+            const int chunk = line & 3, r = valid + (line >> 2);
+            *reinterpret_cast<int4*>(ga + chunk * 8192 + r * 128 + v16 * 16) = make_int4(0, 0, 0, 0);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (!leader) {
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(ready_bar(s), peer));
+          } else {
+            if (lane == 0) {
+              ok = mbar_wait_poll(ready_bar(s), ph, p.mbar_limit);
+              if (!ok) {
+                report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1400 + s, 0, 0);
+                *abort_flag = 1;
+              }
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            tcgen05_fence_after_sync();
+            if (lane == 0) issue_stage(it, tmem_d, ksteps, kb == 0);
+          }
+          ++it;
+        }
+      }
       if (leader && lane == 0) {
         if (tl.kblocks > 0) {
           umma_commit_pair(acc_full_bar(as));
@@ -307,6 +343,14 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
         }
       }
       __syncwarp();
+    }
+    if (counting && leader && lane == 0) {
+      prof_add(kProfLoopCycles, clock64() - loop_c0);
+      prof_add(kProfLoopNs, static_cast<long long>(global_timer_ns() - loop_n0));
+      prof_add(kProfFullWait, full_wait);
+      prof_add(kProfAccWait, acc_wait);
+      prof_add(kProfKBlocks, it);
+      prof_add(kProfTiles, tcount);
     }
     if (leader && lane == 0 && *abort_flag) {
       umma_commit_pair(drain_bar);

@@ -367,8 +367,24 @@ void FusedRank::dequant(const int* plan, int j, int b, bool with_g, cudaStream_t
   ++launches_;
 }
 
-void FusedRank::launch_gemm(int mode, const GemmParams& p, const CUtensorMap& a, const CUtensorMap& b,
+void FusedRank::set_pipeline_counters(c10::optional<torch::Tensor> counters) {
+  if (!counters.has_value()) {
+    prof_ = torch::Tensor();
+    return;
+  }
+  const torch::Tensor& t = *counters;
+  expect(t.is_cuda() && t.scalar_type() == torch::kInt64 && t.is_contiguous() && t.dim() == 3 && t.size(0) == 6 &&
+             t.size(1) >= num_sms_ && t.size(2) == kProfSlots,
+         "pipeline counters must be a contiguous CUDA int64 [6, >= num_sms, 8] tensor");
+  prof_ = t;
+}
+
+void FusedRank::launch_gemm(int mode, const GemmParams& p0, const CUtensorMap& a, const CUtensorMap& b,
                             cudaStream_t st) {
+  GemmParams p = p0;
+  if (prof_.defined())
+    p.prof = reinterpret_cast<unsigned long long*>(prof_.data_ptr<int64_t>()) +
+             static_cast<size_t>(mode) * prof_.size(1) * kProfSlots;
   if (cta_pairs_) launch_grouped_gemm_pair(mode, p, a, b, num_sms_, st);
   else launch_grouped_gemm(mode, p, a, b, num_sms_, st);
   ++launches_;

@@ -64,6 +64,10 @@ class FusedRank {
   std::vector<int64_t> plan_header() const { return std::vector<int64_t>(host_header_, host_header_ + 16); }
   int64_t plan_ints() const { return lay_.total; }
   int64_t launches() const { return launches_; }
+  // Turns the GEMM kernels' pipeline counters on: `counters` is a zeroed int64 CUDA tensor [6 modes, num_sms, 8]
+  // (slots: ProfSlot in gemm/grouped_gemm.cuh) that every later GEMM launch adds to. An undefined tensor turns
+  // them off again. Diagnostics only: the counting costs a few clock reads per k-block.
+  void set_pipeline_counters(c10::optional<torch::Tensor> counters);
   // Debug views of the local scratch (tests compare them with the torch reference).
   torch::Tensor act() const { return act_[0]; }
   torch::Tensor h() const { return h_[0]; }
@@ -111,6 +115,7 @@ class FusedRank {
   int64_t cur_slices_ = 0;
   int64_t cur_rows_ = 0;      // T*K of the current pass
   int64_t launches_ = 0;
+  torch::Tensor prof_;
 };
 
 // Symmetric arena helpers (cudaMalloc + CUDA IPC), one arena per rank.

@@ -103,6 +103,33 @@ def launches() -> int:
     return sum(int(ws.rank.launches()) for ws in _workspaces.values() if ws.rank is not None)
 
 
+PIPELINE_COUNTER_SLOTS = ("loop_cycles", "loop_ns", "producer_wait_free_stage", "mma_wait_filled_stage",
+                          "mma_wait_accumulator", "k_blocks", "epilogue_wait_accumulator", "tiles")
+GEMM_MODE_NAMES = ("swiglu", "down_fwd", "down_dw", "dswiglu", "dx", "tgmm")
+
+
+def pipeline_counters(enable: bool = True) -> list:
+    """Turns the GEMM kernels' in-kernel pipeline counters on (or off) for every cached workspace.
+
+    Returns one zeroed int64 tensor `[6 modes, CTAs, 8 slots]` per workspace (slot names:
+    `PIPELINE_COUNTER_SLOTS`); every later GEMM launch adds its CTAs' cycle counts to it. The counters say which
+    side of the operand ring waits for the other (loads or MMAs) and, from cycles / nanoseconds, the SM clock the
+    kernels really ran at. Diagnostics: counting costs a few clock reads per k-block.
+    """
+    out = []
+    for ws in _workspaces.values():
+        if ws.rank is None:
+            continue
+        if not enable:
+            ws.rank.set_pipeline_counters(None)
+            continue
+        t = torch.zeros(6, max(148, torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count),
+                        len(PIPELINE_COUNTER_SLOTS), dtype=torch.int64, device="cuda")
+        ws.rank.set_pipeline_counters(t)
+        out.append(t)
+    return out
+
+
 def nvtx(name: str):
     from ..utils.nvtx import nvtx_range
 
