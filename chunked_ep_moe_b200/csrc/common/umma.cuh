@@ -269,6 +269,15 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
                : "memory");
 }
 
+// One instruction that arrives on the barrier at offset `cta_addr` in BOTH CTAs of the pair once every pair MMA issued
+// so far has completed (the two-instruction form costs the issuing thread ~100 more cycles per k-block).
+__device__ __forceinline__ void umma_commit_pair_both(uint32_t cta_addr) {
+  const uint16_t both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(cta_addr), "h"(both)
+               : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // TMEM -> registers: 32 lanes x 32 consecutive fp32 columns (thread t reads lane base+t)
 // ---------------------------------------------------------------------------------------------

@@ -242,8 +242,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
           umma_bf16_pair(tmem_d, da + ((k * kDescStepA) >> 4), db + ((k * kDescStepB) >> 4), idesc,
                          (!first_kblock || k > 0) ? 1u : 0u);
       }
-      umma_commit_pair(empty_bar(s));
-      umma_commit_pair(map_to_cta(empty_bar(s), peer));
+      umma_commit_pair_both(empty_bar(s));
     };
     for (int t = first_tile; t < num_tiles && !*abort_flag && (kRelay || leader); t += tile_step, ++tcount) {
       const Tile tl = decode_pair_tile<MODE>(p, t, num_entries, rank);
@@ -335,8 +334,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
       }
       if (leader && lane == 0) {
         if (tl.kblocks > 0) {
-          umma_commit_pair(acc_full_bar(as));
-          umma_commit_pair(map_to_cta(acc_full_bar(as), peer));
+          umma_commit_pair_both(acc_full_bar(as));
         } else {
           mbar_arrive(acc_full_bar(as));  // empty group: both epilogues write zeros
           mbar_arrive_cluster(map_to_cta(acc_full_bar(as), peer));

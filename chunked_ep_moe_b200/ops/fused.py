@@ -103,6 +103,46 @@ def launches() -> int:
     return sum(int(ws.rank.launches()) for ws in _workspaces.values() if ws.rank is not None)
 
 
+def expected_launches(num_slices: int, fp8: bool = False) -> int:
+    """Kernels one forward+backward of the fused layer launches on a rank that loops `num_slices` slices.
+
+    Forward: sort (3) + plan build + pass begin + per slice (put, swiglu, down+combine, slice done) + combine reduce.
+    Backward: pass begin + per slice (put, swiglu+h, down->d_weight/dy, dswiglu, dW_down, dx+combine, dW_up, slice
+    done) + combine reduce. The fp8 wire adds one dequantisation kernel per slice and pass.
+    """
+    per_slice = 12 + (2 if fp8 else 0)
+    return 8 + per_slice * num_slices
+
+
+def memory_plan(world: int, experts: int, top_k: int, tokens_per_rank: int, hidden: int, ffn: int, slice_size: int,
+                fp8: bool = False, tk_cap: int | None = None) -> dict:
+    """Bytes one rank of the fused path holds, by purpose (no GPU needed: sizes come from the arena layout).
+
+    `tk_cap` is the workspace capacity in token copies (default `tokens_per_rank * top_k`).
+    """
+    ext = _build.load()
+    L = experts // world
+    tk = tokens_per_rank * top_k if tk_cap is None else tk_cap
+    S, D, F = slice_size, hidden, ffn
+    arena = int(ext.arena_bytes(world, L, S, D, tk, fp8))
+    scratch = 2 * (S * F * 2 + S * 2 * F * 2 + S * D * 2 + S * 2 * F * 2 + S * (D // 256) * 4)  # act, h, dy, dh, dwp x2
+    carry = 2 * (D * 2 * F + F * D) * 4
+    weights = L * (D * 2 * F + F * D) * 2
+    max_slices = max(1, math.ceil(world * tk / S)) + 1
+    plan = int(ext.plan_layout(world, L, S, max_slices)["total"]) * 4
+    saved = tokens_per_rank * D * 2 + tk * 4 * 3 + plan  # x, router weights, order, inverse order, plan tables
+    out = {
+        "arena (slice buffers x2 for x and g, return rows, counters, traffic matrix)": arena,
+        "scratch (act, h, dy, dh, d_weight partials; two slices in flight)": scratch,
+        "weight-gradient carry tiles (fp32, two per matrix)": carry,
+        "expert weights (bf16)": weights,
+        "expert weight gradients (bf16)": weights,
+        "saved for backward (x, router weights, sort order, plan)": saved,
+    }
+    out["total"] = sum(out.values())
+    return out
+
+
 PIPELINE_COUNTER_SLOTS = ("loop_cycles", "loop_ns", "producer_wait_free_stage", "mma_wait_filled_stage",
                           "mma_wait_accumulator", "k_blocks", "epilogue_wait_accumulator", "tiles")
 GEMM_MODE_NAMES = ("swiglu", "down_fwd", "down_dw", "dswiglu", "dx", "tgmm")

@@ -48,3 +48,35 @@ def test_clock_sample_parser(tmp_path):
     got = sampler.stop()
     assert got["sm_mhz"] == 1340.0 and got["sm_max_mhz"] == 1965.0
     assert got["reasons"] == ["sw_power_cap"] and got["samples"] == 3
+
+
+def test_compile_report_pieces():
+    """The compile-only report's parser, launch formula and memory plan (no nvcc run, no GPU)."""
+    sys.path.insert(0, os.path.join(ROOT, "bench"))
+    import compile_report
+    from chunked_ep_moe_b200.ops import fused
+
+    text = """ptxas info    : Compiling entry function '_Zk1' for 'sm_100a'
+ptxas info    : Function properties for _Zk1
+    0 bytes stack frame, 8 bytes spill stores, 4 bytes spill loads
+ptxas info    : Used 112 registers, used 1 barriers, 16 bytes smem
+ptxas info    : Compiling entry function '_Zk2' for 'sm_100a'
+ptxas info    : Function properties for _Zk2
+    0 bytes stack frame, 0 bytes spill stores, 0 bytes spill loads
+ptxas info    : Used 32 registers"""
+    assert compile_report.parse_ptxas(text) == [("_Zk1", 112, 12, 16), ("_Zk2", 32, 0, 0)]
+    assert compile_report.short("void cem::<unnamed>::grouped_gemm_kernel<(cem::GemmMode)3>(cem::GemmParams)") == \
+        "grouped_gemm_kernel<mode 3>"
+
+    # 8 slices: the 1-GPU bench layout launches 104 kernels per step, 9 slices (8 GPUs, random routing) 116
+    assert fused.expected_launches(8) == 104 and fused.expected_launches(9) == 116
+    assert fused.expected_launches(8, fp8=True) == 104 + 16
+
+    plan = fused.memory_plan(world=8, experts=256, top_k=8, tokens_per_rank=8192, hidden=7168, ffn=2048,
+                             slice_size=8192)
+    assert plan["expert weights (bf16)"] == 32 * (7168 * 4096 + 2048 * 7168) * 2
+    assert plan["total"] == sum(v for k, v in plan.items() if k != "total")
+    assert plan["total"] < 16 * 2**30, "the DeepSeek-V3-size layer on 8 ranks fits in a fraction of 180 GB"
+    work = compile_report.work_report(8, 256, 8, 8192, 7168, 2048, 8192, False)
+    assert abs(work["GEMM TFLOP per rank per step"] - 23.09) < 0.01
+    assert work["kernel launches per step"] == 104

@@ -101,6 +101,58 @@ def test_single_rank_layer_matches_oracle(group_rows, slice_size, stripe):
     _close(ds.grad.cpu(), want["dw_down"], "dw_down")
 
 
+def test_launch_count_matches_the_formula():
+    """One forward+backward launches exactly `expected_launches(slices)` kernels (what bench.py reports)."""
+    from chunked_ep_moe_b200.ops import fused
+
+    torch.manual_seed(0)
+    T, D, F, E, K, S = 192, 256, 256, 4, 2, 128
+    cfg = ChunkedMoEConfig(num_experts=E, top_k=K, slice_size=S, transport="nvshmem", expert_compute="fused",
+                           stripe_width=64)
+    x = torch.randn(T, D, device="cuda").bfloat16().requires_grad_(True)
+    ids = torch.stack([torch.randperm(E, device="cuda")[:K] for _ in range(T)]).int()
+    w = torch.rand(T, K, device="cuda").requires_grad_(True)
+    w_up = (torch.randn(E, D, 2 * F, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    w_down = (torch.randn(E, F, D, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    chunked_moe(x, ids, w, w_up, w_down, cfg, None).sum().backward()  # builds the workspace
+    before = fused.launches()
+    chunked_moe(x, ids, w, w_up, w_down, cfg, None).sum().backward()
+    torch.cuda.synchronize()
+    slices = -(-T * K // S)
+    assert fused.launches() - before == fused.expected_launches(slices)
+
+
+def test_pipeline_counters_count_every_k_block():
+    """The GEMM kernels' own counters: k-blocks issued = tiles x K/64 for the forward modes, and cycles were counted."""
+    from chunked_ep_moe_b200.ops import fused
+
+    torch.manual_seed(0)
+    T, D, F, E, K, S = 256, 512, 256, 2, 1, 256
+    cfg = ChunkedMoEConfig(num_experts=E, top_k=K, slice_size=S, transport="nvshmem", expert_compute="fused",
+                           stripe_width=64)
+    x = torch.randn(T, D, device="cuda").bfloat16()
+    ids = (torch.arange(T, device="cuda") % E).int().reshape(T, K)  # 128 rows per expert: one full row tile each
+    w = torch.ones(T, K, device="cuda")
+    w_up = (torch.randn(E, D, 2 * F, device="cuda") * 0.05).bfloat16()
+    w_down = (torch.randn(E, F, D, device="cuda") * 0.05).bfloat16()
+    chunked_moe(x, ids, w, w_up, w_down, cfg, None)  # builds the workspace
+    counters = fused.pipeline_counters(True)
+    try:
+        chunked_moe(x, ids, w, w_up, w_down, cfg, None)
+        torch.cuda.synchronize()
+    finally:
+        fused.pipeline_counters(False)
+    slot = {n: i for i, n in enumerate(fused.PIPELINE_COUNTER_SLOTS)}
+    total = sum(t for t in counters).sum(1)  # [modes, slots]
+    row_tiles = T * K // 128
+    swiglu, down = fused.GEMM_MODE_NAMES.index("swiglu"), fused.GEMM_MODE_NAMES.index("down_fwd")
+    assert int(total[swiglu, slot["tiles"]]) == row_tiles * (2 * F // 256)
+    assert int(total[swiglu, slot["k_blocks"]]) == row_tiles * (2 * F // 256) * (D // 64)
+    assert int(total[down, slot["k_blocks"]]) == row_tiles * (D // 256) * (F // 64)
+    assert int(total[swiglu, slot["loop_cycles"]]) > 0 and int(total[swiglu, slot["loop_ns"]]) > 0
+    assert int(total[fused.GEMM_MODE_NAMES.index("tgmm"), slot["k_blocks"]]) == 0  # no backward ran
+
+
 def test_fused_expert_compute_on_a_collective_transport():
     """`expert_compute="fused"` under `transport="ragged_a2a"`: the library exchange feeds the sm_100a kernels."""
     gen = torch.Generator().manual_seed(4)
