@@ -68,8 +68,8 @@ class RMSNorm(nn.Module):
         self.eps = eps
 
     def forward(self, x):
-        xf = x.float()
-        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)).to(x.dtype) * self.weight
+        # fp32 statistics, output in x's dtype; one fused kernel on CUDA instead of six elementwise ones
+        return F.rms_norm(x, (x.shape[-1],), self.weight, self.eps)
 
 
 def rope_tables(seq_len: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
@@ -79,10 +79,12 @@ def rope_tables(seq_len: int, head_dim: int, theta: float, device) -> tuple[torc
 
 
 def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-    """x: [B, H, S, hd]; rotates pairs (even, odd) of the head dimension."""
-    xf = x.float()
-    x1, x2 = xf[..., 0::2], xf[..., 1::2]
-    out = torch.stack((x1 * cos - x2 * sin, x1 * sin + x2 * cos), dim=-1).flatten(-2)
+    """x: [B, H, S, hd]; rotates pairs (even, odd) of the head dimension, in fp32.
+
+    Written as one complex multiplication ((x1 + i x2)(cos + i sin)): three kernels instead of eight.
+    """
+    xc = torch.view_as_complex(x.float().reshape(*x.shape[:-1], -1, 2))
+    out = torch.view_as_real(xc * torch.complex(cos, sin)).flatten(-2)
     return out.to(x.dtype)
 
 

@@ -45,7 +45,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--dense-ffn", type=int, default=4096)
     ap.add_argument("--top-k", type=int, default=6)
     ap.add_argument("--vocab", type=int, default=32000)
-    ap.add_argument("--slice-size", type=int, default=8192)
+    ap.add_argument("--slice-size", type=int, default=16384,
+                    help="rows per slice; with these small experts (D=1024, F=512) larger slices mean fewer, fuller "
+                         "launches (measured on one GPU: 58 ms per step at 8192, 42 ms at 16384, 41 ms at 49152)")
     ap.add_argument("--comm-dtype", default=None, choices=[None, "float8_e4m3fn"])
     ap.add_argument("--save", default=None, help="directory to write a checkpoint to after the last step")
     ap.add_argument("--resume", default=None, help="directory to resume from")
