@@ -212,6 +212,16 @@ __device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uin
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 
+// Tiled 3-D load for MN-major operands: the matrix [rows, cols] is described as (64 columns, rows, cols / 64), so one
+// instruction brings `chunks` 64-column chunks of the same rows, each as its own [rows][128 B] block in shared memory.
+// x is always 0 (16-byte rule), y the first row, z the first 64-column chunk.
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(0), "r"(y), "r"(z)
+      : "memory");
+}
+
 // Pair-aware TMA load: the data lands in THIS CTA's shared memory, the completion bytes are credited to a
 // barrier that may belong to the other CTA of the pair (the pair leader collects both halves of a stage).
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* map, uint32_t cluster_bar,
@@ -219,6 +229,14 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtens
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const CUtensorMap* map, uint32_t cluster_bar,
+                                                 int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(0), "r"(y), "r"(z)
       : "memory");
 }
 

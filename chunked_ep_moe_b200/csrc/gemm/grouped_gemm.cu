@@ -29,25 +29,20 @@ template <int MODE>
 __device__ __forceinline__ void issue_kblock(const GemmParams& p, const Tile& tl, int kb, const CUtensorMap* map_a,
                                              const CUtensorMap* map_b, uint32_t sa, uint32_t sb, uint32_t bar) {
   using Traits = ModeTraits<MODE>;
-  auto go = [&](const CUtensorMap* map, uint32_t dst, int x, int y) { tma_load_2d(dst, map, bar, x, y); };
   if constexpr (Traits::kAMn) {
-    // lhs [S, M]: k runs over rows; two 64-column chunks of the 128-wide row tile.
-    go(map_a, sa, tl.m * kBlockM, tl.row0 + kb * kBlockK);
-    go(map_a, sa + 8192, tl.m * kBlockM + 64, tl.row0 + kb * kBlockK);
+    // lhs [S, M]: k runs over rows; the 128-wide row tile is two 64-column chunks, one 3-D copy.
+    tma_load_3d(sa, map_a, bar, tl.row0 + kb * kBlockK, tl.m * (kBlockM / 64));
   } else {
-    go(map_a, sa, kb * kBlockK, tl.row0);
+    tma_load_2d(sa, map_a, bar, kb * kBlockK, tl.row0);
   }
   if constexpr (MODE == kModeTgmm) {
-#pragma unroll
-    for (int c = 0; c < 4; ++c) go(map_b, sb + c * 8192, tl.n * kBlockN + c * 64, tl.row0 + kb * kBlockK);
+    tma_load_3d(sb, map_b, bar, tl.row0 + kb * kBlockK, tl.n * (kBlockN / 64));
   } else if constexpr (Traits::kBMn) {
-    // weights [L*K, N]: four 64-column chunks of the 256-wide column tile.
-#pragma unroll
-    for (int c = 0; c < 4; ++c)
-      go(map_b, sb + c * 8192, tl.n * kBlockN + c * 64, tl.g * p.b_group_rows + kb * kBlockK);
+    // weights [L*K, N]: the 256-wide column tile is four 64-column chunks, one 3-D copy.
+    tma_load_3d(sb, map_b, bar, tl.g * p.b_group_rows + kb * kBlockK, tl.n * (kBlockN / 64));
   } else {
     // weights [L*N, K] read as K-major B: 256 rows x 64 k.
-    go(map_b, sb, kb * kBlockK, tl.g * p.b_group_rows + tl.n * kBlockN);
+    tma_load_2d(sb, map_b, bar, kb * kBlockK, tl.g * p.b_group_rows + tl.n * kBlockN);
   }
 }
 

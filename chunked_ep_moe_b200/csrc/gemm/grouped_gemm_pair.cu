@@ -65,24 +65,18 @@ __device__ __forceinline__ void issue_pair_kblock(const GemmParams& p, const Til
                                                   const CUtensorMap* map_a, const CUtensorMap* map_b, uint32_t sa,
                                                   uint32_t sb, uint32_t bar) {
   using Traits = ModeTraits<MODE>;
-  auto tma_load_2d = [&](uint32_t dst, const CUtensorMap* map, uint32_t b, int x, int y) {
-    if constexpr (MODE == kModeTgmm) cem::tma_load_2d(dst, map, b, x, y); else tma_load_2d_pair(dst, map, b, x, y);
-  };
-  if constexpr (Traits::kAMn) {
-    tma_load_2d(sa, map_a, bar, tl.m * kBlockM, tl.row0 + kb * kBlockK);
-    tma_load_2d(sa + 8192, map_a, bar, tl.m * kBlockM + 64, tl.row0 + kb * kBlockK);
-  } else {
-    tma_load_2d(sa, map_a, bar, kb * kBlockK, tl.row0);
-  }
-  const int col0 = tl.n * kBlockN + rank * (kBlockN / 2);  // this CTA's half of the 256-wide column tile
+  const int chunk0 = tl.n * (kBlockN / 64) + rank * (kBlockN / 128);  // this CTA's half of the 256-wide column tile
   if constexpr (MODE == kModeTgmm) {
-    tma_load_2d(sb, map_b, bar, col0, tl.row0 + kb * kBlockK);
-    tma_load_2d(sb + 8192, map_b, bar, col0 + 64, tl.row0 + kb * kBlockK);
-  } else if constexpr (Traits::kBMn) {
-    tma_load_2d(sb, map_b, bar, col0, tl.g * p.b_group_rows + kb * kBlockK);
-    tma_load_2d(sb + 8192, map_b, bar, col0 + 64, tl.g * p.b_group_rows + kb * kBlockK);
+    // relay scheme: plain loads on this CTA's own barrier; A and B are both two 64-column chunks
+    tma_load_3d(sa, map_a, bar, tl.row0 + kb * kBlockK, tl.m * (kBlockM / 64));
+    tma_load_3d(sb, map_b, bar, tl.row0 + kb * kBlockK, chunk0);
   } else {
-    tma_load_2d(sb, map_b, bar, kb * kBlockK, tl.g * p.b_group_rows + col0);  // 128-row box
+    tma_load_2d_pair(sa, map_a, bar, kb * kBlockK, tl.row0);
+    if constexpr (Traits::kBMn) {
+      tma_load_3d_pair(sb, map_b, bar, tl.g * p.b_group_rows + kb * kBlockK, chunk0);
+    } else {
+      tma_load_2d_pair(sb, map_b, bar, kb * kBlockK, tl.g * p.b_group_rows + tl.n * kBlockN + rank * (kBlockN / 2));  // 128-row box
+    }
   }
 }
 

@@ -141,19 +141,21 @@ FusedRank::FusedRank(int P, int L, int me, int S, int D, int F, int K, int strip
   }
   tables_ = torch::from_blob(host.data(), {static_cast<int64_t>(kNumTables), P}, torch::kInt64).clone().to(torch::kCUDA);
 
-  // TMA descriptors of the local buffers. K-major A tiles are 128 rows, MN-major tiles 64 rows (k).
+  // TMA descriptors of the local buffers. K-major A tiles are 128 rows, MN-major tiles 64 rows (k) of several
+  // 64-column chunks brought by one 3-D copy (a CTA of a pair loads half of the 256-wide column tile).
+  const uint32_t mn_chunks_b = cta_pairs_ ? 2 : 4;
   for (int b = 0; b < 2; ++b) {
     const void* xb = arena_ + arena_lay_.xbuf + static_cast<size_t>(b) * S * D * 2;
     map_x_k_[b] = make_bf16_map_2d(xb, S, D, 128);
-    map_x_mn_[b] = make_bf16_map_2d(xb, S, D, 64);
+    map_x_mn_[b] = make_bf16_map_chunked(xb, S, D, 64, 2);  // weight-gradient lhs: 128 columns per tile
   }
   for (int q = 0; q < 2; ++q) {
     map_act_k_[q] = make_bf16_map_2d(act_[q].data_ptr(), S, F, 128);
-    map_act_mn_[q] = make_bf16_map_2d(act_[q].data_ptr(), S, F, 64);
+    map_act_mn_[q] = make_bf16_map_chunked(act_[q].data_ptr(), S, F, 64, 2);
     map_dy_k_[q] = make_bf16_map_2d(dy_[q].data_ptr(), S, D, 128);
-    map_dy_mn_[q] = make_bf16_map_2d(dy_[q].data_ptr(), S, D, 64);
+    map_dy_mn_[q] = make_bf16_map_chunked(dy_[q].data_ptr(), S, D, 64, mn_chunks_b);  // weight-gradient rhs
     map_dh_k_[q] = make_bf16_map_2d(dh_[q].data_ptr(), S, 2 * F, 128);
-    map_dh_mn_[q] = make_bf16_map_2d(dh_[q].data_ptr(), S, 2 * F, 64);
+    map_dh_mn_[q] = make_bf16_map_chunked(dh_[q].data_ptr(), S, 2 * F, 64, mn_chunks_b);
   }
 
   if (use_comm_stream_) {
@@ -329,16 +331,17 @@ GemmParams FusedRank::base_params(const int* plan, int j) const {
   return p;
 }
 
-const CUtensorMap& FusedRank::weight_map(const torch::Tensor& w, uint32_t box_rows) {
+const CUtensorMap& FusedRank::weight_map(const torch::Tensor& w, uint32_t box_rows, uint32_t chunks) {
   // Keyed by address AND geometry: a freed tensor's address can come back with another shape.
-  auto key = std::make_tuple(static_cast<const void*>(w.data_ptr()), box_rows,
+  auto key = std::make_tuple(static_cast<const void*>(w.data_ptr()), box_rows | (chunks << 16),
                              static_cast<int64_t>(w.size(0)) * w.size(1), static_cast<int64_t>(w.size(2)));
   auto it = weight_maps_.find(key);
   if (it == weight_maps_.end()) {
     if (weight_maps_.size() > 4096) weight_maps_.clear();
     // [L, R, C] viewed as the 2-D matrix [L*R, C]; tiles never straddle experts because R % box_rows == 0.
-    it = weight_maps_.emplace(key, make_bf16_map_2d(w.data_ptr(), static_cast<uint64_t>(w.size(0)) * w.size(1),
-                                                    static_cast<uint64_t>(w.size(2)), box_rows)).first;
+    const uint64_t rows = static_cast<uint64_t>(w.size(0)) * w.size(1), cols = static_cast<uint64_t>(w.size(2));
+    it = weight_maps_.emplace(key, chunks ? make_bf16_map_chunked(w.data_ptr(), rows, cols, box_rows, chunks)
+                                          : make_bf16_map_2d(w.data_ptr(), rows, cols, box_rows)).first;
   }
   return it->second;
 }
@@ -432,7 +435,7 @@ void FusedRank::compute_forward(int64_t j, torch::Tensor plan, torch::Tensor w_u
     p.ld0 = F_;
     p.out1 = nullptr;
     p.ld1 = 2 * F_;
-    launch_gemm(kModeSwiglu, p, map_x_k_[b], weight_map(w_up, 64), st);
+    launch_gemm(kModeSwiglu, p, map_x_k_[b], weight_map(w_up, 64, cta_pairs_ ? 2 : 4), st);
   }
   {
     GemmParams p = base_params(pl, static_cast<int>(j));
@@ -443,7 +446,7 @@ void FusedRank::compute_forward(int64_t j, torch::Tensor plan, torch::Tensor w_u
     p.peer_rows = table<__nv_bfloat16>(kTabRet);
     p.peer_count = table<uint32_t>(kTabCount);
     p.ld0 = D_;
-    launch_gemm(kModeDownFwd, p, map_act_k_[q], weight_map(w_down, 64), st);
+    launch_gemm(kModeDownFwd, p, map_act_k_[q], weight_map(w_down, 64, cta_pairs_ ? 2 : 4), st);
   }
   if (async) {
     cuda_check(cudaEventRecord(ev_down_[q], st), "event record");
@@ -485,7 +488,7 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
     p.ld0 = F_;
     p.out1 = reinterpret_cast<__nv_bfloat16*>(h_[q].data_ptr());
     p.ld1 = 2 * F_;
-    launch_gemm(kModeSwiglu, p, map_x_k_[b], weight_map(w_up, 64), st);
+    launch_gemm(kModeSwiglu, p, map_x_k_[b], weight_map(w_up, 64, cta_pairs_ ? 2 : 4), st);
   }
   {  // remat of y, folded into d_weight partials; dy = w * g
     GemmParams p = base_params(pl, static_cast<int>(j));
@@ -498,7 +501,7 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
     p.ld0 = D_;
     p.dwp = dwp_[q].data_ptr<float>();
     p.dwp_tiles = dwp_tiles;
-    launch_gemm(kModeDownDw, p, map_act_k_[q], weight_map(w_down, 64), st);
+    launch_gemm(kModeDownDw, p, map_act_k_[q], weight_map(w_down, 64, cta_pairs_ ? 2 : 4), st);
   }
   if (async) {
     cuda_check(cudaEventRecord(ev_dd_[q], st), "event record");

@@ -78,7 +78,8 @@ class FusedRank {
   void end_pass(int64_t n_slices);
   void join_streams(bool backward);
   GemmParams base_params(const int* plan, int j) const;
-  const CUtensorMap& weight_map(const torch::Tensor& w, uint32_t box_rows);
+  // `chunks` > 0: the MN-major description (64-column chunks, `chunks` of them per copy); 0: plain 2-D boxes.
+  const CUtensorMap& weight_map(const torch::Tensor& w, uint32_t box_rows, uint32_t chunks = 0);
   void dequant(const int* plan, int j, int b, bool with_g, cudaStream_t st);
   void launch_gemm(int mode, const GemmParams& p, const CUtensorMap& a, const CUtensorMap& b, cudaStream_t st);
 

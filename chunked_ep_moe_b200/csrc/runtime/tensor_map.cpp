@@ -47,4 +47,23 @@ CUtensorMap make_bf16_map_2d(const void* base, uint64_t rows, uint64_t cols, uin
   return map;
 }
 
+CUtensorMap make_bf16_map_chunked(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t chunks) {
+  if (reinterpret_cast<uintptr_t>(base) % 16 != 0) throw std::runtime_error("tensor map base must be 16-byte aligned");
+  if (cols % 64 != 0) throw std::runtime_error("chunked tensor map needs a multiple of 64 columns");
+  if (box_rows == 0 || box_rows > 256 || chunks == 0 || chunks > 256)
+    throw std::runtime_error("tensor map box rows and chunks must be in [1, 256]");
+  CUtensorMap map;
+  const cuuint64_t dims[3] = {64, rows, cols / 64};
+  const cuuint64_t strides[2] = {cols * 2, 128};
+  const cuuint32_t box[3] = {64, box_rows, chunks};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  CUresult res = encode_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,
+                             elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS)
+    throw std::runtime_error("cuTensorMapEncodeTiled (chunked) failed with CUresult " +
+                             std::to_string(static_cast<int>(res)));
+  return map;
+}
+
 }  // namespace cem
