@@ -180,14 +180,28 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
     const __nv_bfloat16* g_row = p.in0 + static_cast<size_t>(grow) * p.ld0 + tl.n * kBlockN;
     __nv_bfloat16* dy_row = p.out0 + static_cast<size_t>(grow) * p.ld0 + tl.n * kBlockN;
     float partial = 0.0f;
+    // The g chunk of the NEXT 32 columns is requested before this chunk's accumulator is waited for, so its global
+    // load latency hides behind the TMEM load and the arithmetic (this epilogue was the mode's bottleneck).
+    int4 gnext[4] = {};
+    if (valid) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) gnext[i] = *reinterpret_cast<const int4*>(g_row + 8 * i);
+    }
 #pragma unroll 1
     for (int c = 0; c < 8; ++c) {
+      int4 gcur[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) gcur[i] = gnext[i];
       tmem_ld_32x32(tacc + c * 32, r);
+      if (valid && c + 1 < 8) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) gnext[i] = *reinterpret_cast<const int4*>(g_row + (c + 1) * 32 + 8 * i);
+      }
       tmem_ld_wait();
       if (valid) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int4 gv = *reinterpret_cast<const int4*>(g_row + c * 32 + 8 * i);
+          const int4 gv = gcur[i];
           const uint32_t gw[4] = {static_cast<uint32_t>(gv.x), static_cast<uint32_t>(gv.y),
                                   static_cast<uint32_t>(gv.z), static_cast<uint32_t>(gv.w)};
           uint32_t o[4];
