@@ -2,7 +2,7 @@
 // reference (which sorts with XLA's argsort and lets XLA own every buffer).
 //
 // Who needs it: code that runs where cudaMalloc is off limits -- inside a region being captured
-// into a CUDA graph, inside a memory-pool or allocator callback, in a process whose memory budget
+// into a CUDA graph, inside a memory-pool or allocator callback, in a process whose memory allowance
 // is fixed up front by another framework, or in a latency-critical loop where an allocation
 // (which may synchronise the device) is not acceptable. Such callers cannot hand the sort its
 // scratch buffer either without allocating it somewhere, so the library carries the scratch

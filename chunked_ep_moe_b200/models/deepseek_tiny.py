@@ -1,7 +1,7 @@
 """DeepSeek-V3-style decoder with chunked expert-parallel MoE layers.
 
 The reference ships only the MoE layer; the model around it lived in an external MaxText branch
-(reference DESIGN.md:230-263: router kept from the host framework — sigmoid scores, routed bias,
+(the reference's top-level design document, lines 230-263: router kept from the host framework — sigmoid scores, routed bias,
 routed scaling, load-balance loss, bias-update counts — then `stripe_weights` + `chunked_moe`).
 This module is that host model written for this framework so the layer can be trained end to end:
 

@@ -1,7 +1,7 @@
 """The allocation-free expert sort, called through its exported C symbol.
 
 Some callers of this library cannot allocate device memory at the point where they need the sort
-(inside a CUDA-graph capture region, under a fixed memory budget owned by another framework, in
+(inside a CUDA-graph capture region, under a fixed memory allowance owned by another framework, in
 an allocator callback). For them the library exports `cem_expert_sort_noalloc`, which runs the same
 sort on a scratch array built into the library. This test loads the shared object with ctypes,
 calls the symbol twice in a row on different inputs (the second call sees the first call's
