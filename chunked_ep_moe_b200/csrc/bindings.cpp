@@ -97,7 +97,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("put_blocks"), py::arg("cta_pairs") = true)
       .def("begin_forward", &cem::FusedRank::begin_forward)
       .def("sort_only", &cem::FusedRank::sort_only)
-      .def("begin_backward", &cem::FusedRank::begin_backward)
+      .def("begin_backward", &cem::FusedRank::begin_backward, py::arg("plan"), py::arg("known_slices") = -1,
+           py::arg("known_rows") = -1)
       .def("put", &cem::FusedRank::put)
       .def("compute_forward", &cem::FusedRank::compute_forward)
       .def("compute_backward", &cem::FusedRank::compute_backward)

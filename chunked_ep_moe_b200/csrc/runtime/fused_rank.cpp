@@ -254,18 +254,27 @@ int64_t FusedRank::begin_forward(torch::Tensor expert_ids, torch::Tensor plan, t
   }
   launch_plan_build(pp, st);
   ++launches_;
-  return begin_backward(plan);
+  return begin_backward(plan, -1, -1);
 }
 
-int64_t FusedRank::begin_backward(torch::Tensor plan) {
+int64_t FusedRank::begin_backward(torch::Tensor plan, int64_t known_slices, int64_t known_rows) {
   cudaStream_t st = current_stream();
   expect_i32(plan, lay_.total, "plan");
-  cuda_check(cudaMemcpyAsync(host_header_, plan.data_ptr(), 16 * sizeof(int32_t), cudaMemcpyDeviceToHost, st),
-             "plan header copy");
-  check_status();  // synchronises the stream: header and status are both on the host now
-  expect(host_header_[4] == 0, "routing needs more slices than the workspace was sized for (max_slices)");
-  cur_slices_ = host_header_[0];
-  cur_rows_ = host_header_[5];
+  if (known_slices >= 0 && known_rows >= 0) {
+    // The caller kept what the forward of this plan read back: no device-to-host copy, no synchronisation, so the
+    // host keeps running ahead of the device through the whole backward. (A recorded kernel error then surfaces at
+    // the next synchronising call: the next forward, or `check_status`.)
+    expect(known_slices <= max_slices_, "slice count exceeds the workspace");
+    cur_slices_ = known_slices;
+    cur_rows_ = known_rows;
+  } else {
+    cuda_check(cudaMemcpyAsync(host_header_, plan.data_ptr(), 16 * sizeof(int32_t), cudaMemcpyDeviceToHost, st),
+               "plan header copy");
+    check_status();  // synchronises the stream: header and status are both on the host now
+    expect(host_header_[4] == 0, "routing needs more slices than the workspace was sized for (max_slices)");
+    cur_slices_ = host_header_[0];
+    cur_rows_ = host_header_[5];
+  }
   launch_pass_begin(plan.data_ptr<int>(), lay_, reinterpret_cast<uint32_t*>(expected_total_.data_ptr()),
                     reinterpret_cast<uint32_t*>(pass_base_.data_ptr()), st);
   ++launches_;

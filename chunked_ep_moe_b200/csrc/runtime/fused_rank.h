@@ -49,7 +49,9 @@ class FusedRank {
                         torch::Tensor counts, bool counts_prefilled);
   // Lockstep harness only: sort + histogram without the exchange (fills order, inv_order, my row of counts).
   void sort_only(torch::Tensor expert_ids, torch::Tensor order, torch::Tensor inv_order, torch::Tensor my_counts);
-  int64_t begin_backward(torch::Tensor plan);
+  // `known_slices`, `known_rows` (T*K): what the forward of the same plan returned / was given; when both are >= 0
+  // the plan header is not read back and the stream is not synchronised.
+  int64_t begin_backward(torch::Tensor plan, int64_t known_slices = -1, int64_t known_rows = -1);
 
   void put(int64_t j, torch::Tensor plan, torch::Tensor order, torch::Tensor x, c10::optional<torch::Tensor> g,
            torch::Tensor w_flat);

@@ -98,6 +98,17 @@ def last_plan_stats(cfg: ChunkedMoEConfig) -> list:
             if ws.rank is not None]
 
 
+def check_status() -> None:
+    """Synchronises and raises if any kernel of a cached workspace recorded an error (a wait that ran out).
+
+    The forward checks on its own (it has to read the slice count back anyway); the backward does not synchronise,
+    so a training loop calls this once per step, before the optimizer consumes the gradients.
+    """
+    for ws in _workspaces.values():
+        if ws.rank is not None:
+            ws.rank.check_status()
+
+
 def launches() -> int:
     """Kernels launched so far by every cached workspace of this process."""
     return sum(int(ws.rank.launches()) for ws in _workspaces.values() if ws.rank is not None)
@@ -208,7 +219,7 @@ class _ChunkedMoEFused(torch.autograd.Function):
         with nvtx("chunked_moe/combine"):
             rank.finish_forward(inv_order, out)
         ctx.save_for_backward(xc, weights, w_up_c, w_down_c, plan, order, inv_order)
-        ctx.cfg, ctx.group, ctx.ws = cfg, group, ws
+        ctx.cfg, ctx.group, ctx.ws, ctx.num_slices = cfg, group, ws, int(n)
         ctx.mark_non_differentiable(expert_ids)
         return out
 
@@ -218,7 +229,8 @@ class _ChunkedMoEFused(torch.autograd.Function):
         rank = ctx.ws.rank
         g = g_out.to(x.dtype).contiguous()
         w_flat = weights.detach().float().reshape(-1).contiguous()
-        n = rank.begin_backward(plan)
+        # The slice count is the forward's: nothing is read back, the host never waits for the device here.
+        n = rank.begin_backward(plan, ctx.num_slices, order.numel())
         dw_up, dw_down = torch.empty_like(w_up), torch.empty_like(w_down)
         if n > 0:
             rank.put(0, plan, order, x, g, w_flat)

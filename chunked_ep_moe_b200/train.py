@@ -131,6 +131,10 @@ def train(args, group=None) -> dict:
             ce, aux = model(tokens, targets)
             ((ce + aux) / accum).backward()
             loss_sum += ce.detach() / accum
+        if args.impl == "fused":
+            from .ops import fused
+
+            fused.check_status()  # the fused backward does not synchronise: surface a recorded kernel error here
         reduce_gradients(model, world, group)
         opt.step()
         for router in model.routers():
