@@ -59,6 +59,32 @@ def reference_unavailable():
     }))
 
 
+def bind_near_gpu(index: int) -> str:
+    """Best effort: run this process (and allocate its pinned buffers) on the CPUs next to GPU `index`.
+
+    Only this process's own CPU affinity changes, nothing of the GPU's. Returns a note for the log; any failure
+    (no NVML, a cpuset that excludes those CPUs) leaves the affinity as it was.
+    """
+    try:
+        import pynvml
+
+        import torch
+
+        pynvml.nvmlInit()
+        uuid = "GPU-" + str(torch.cuda.get_device_properties(index).uuid)  # CUDA and NVML may number GPUs differently
+        handle = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        near = {64 * w + b for w, word in enumerate(words) for b in range(64) if (word >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        both = near & allowed
+        if not both or both == allowed:
+            return "cpu affinity unchanged"
+        os.sched_setaffinity(0, both)
+        return f"bound to {len(both)} CPUs near GPU {index}"
+    except Exception as exc:  # noqa: BLE001 - purely advisory
+        return f"cpu affinity unchanged ({type(exc).__name__})"
+
+
 class ClockSampler:
     """Samples nvidia-smi clocks and throttle reasons while the timed region runs (read-only queries)."""
 
@@ -143,6 +169,7 @@ def main():
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run for N > 1")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    affinity_note = bind_near_gpu(local_rank)
     group = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -214,7 +241,8 @@ def main():
         stage_inputs(slot ^ 1)  # the next step's copy overlaps this step's compute
         x, ids, weights = slots[slot]
         out, dx, dw = step(x.detach(), ids, weights.detach())
-        loss_h.copy_((out.float().mean() + dx.float().mean()).reshape(1), non_blocking=True)
+        # fp32 accumulation inside the reduction kernels: no fp32 copies of the two [T, D] tensors
+        loss_h.copy_((out.mean(dtype=torch.float32) + dx.mean(dtype=torch.float32)).reshape(1), non_blocking=True)
         consumed[slot] = torch.cuda.Event()
         consumed[slot].record(cur)
         cur.synchronize()  # the host owns the step's result before the next step starts
@@ -339,6 +367,7 @@ def main():
             "clocks": clocks,
             "e2e": e2e,
             "gpu_launches": int(n_launch),
+            "host": affinity_note,
             "local_only_ms_per_step": local_ms,
             "exposed_a2a_ms_per_step": (ms - local_ms) if local_ms is not None else (0.0 if world == 1 else None),
         }
