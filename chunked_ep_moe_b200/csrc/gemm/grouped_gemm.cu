@@ -257,10 +257,13 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
           // Each k row is one 128-byte line per 64-column chunk.
           uint8_t* ga = smem_gen + s * kStageBytes;
           const int zrows = ksteps * kUmmaK - valid;
-          for (int idx = lane; idx < zrows * 6 * 8; idx += 32) {
-            const int v16 = idx & 7, line = idx >> 3;
-            const int chunk = line % 6, r = valid + line / 6;
-            *reinterpret_cast<int4*>(ga + chunk * 8192 + r * 128 + v16 * 16) = make_int4(0, 0, 0, 0);
+          // A k row is 48 16-byte pieces (6 chunks x 8): lane i clears piece i of chunks 0-3, lanes 0-15 also piece
+          // 32+i of chunks 4-5. Two stores per row, no index arithmetic in the loop.
+          uint8_t* lo = ga + (lane >> 3) * 8192 + (lane & 7) * 16 + valid * 128;
+          uint8_t* hi = lo + 4 * 8192;
+          for (int r = 0; r < zrows; ++r, lo += 128, hi += 128) {
+            *reinterpret_cast<int4*>(lo) = make_int4(0, 0, 0, 0);
+            if (lane < 16) *reinterpret_cast<int4*>(hi) = make_int4(0, 0, 0, 0);
           }
           fence_proxy_async_smem();
           __syncwarp();

@@ -301,11 +301,9 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
           // Zero this CTA's rows [valid, ksteps*16) in its four 64-column chunks (2 of A, 2 of B).
           uint8_t* ga = smem_gen + s * kPairStageBytes;
           const int zrows = ksteps * kUmmaK - valid;
-          for (int idx = lane; idx < zrows * 4 * 8; idx += 32) {
-            const int v16 = idx & 7, line = idx >> 3;
-            const int chunk = line & 3, r = valid + (line >> 2);
-            *reinterpret_cast<int4*>(ga + chunk * 8192 + r * 128 + v16 * 16) = make_int4(0, 0, 0, 0);
-          }
+          // A k row is 32 16-byte pieces here (4 chunks x 8): lane i clears piece i, one store per row.
+          uint8_t* piece = ga + (lane >> 3) * 8192 + (lane & 7) * 16 + valid * 128;
+          for (int r = 0; r < zrows; ++r, piece += 128) *reinterpret_cast<int4*>(piece) = make_int4(0, 0, 0, 0);
           fence_proxy_async_smem();
           __syncwarp();
           if (!leader) {
