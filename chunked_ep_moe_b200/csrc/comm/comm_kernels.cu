@@ -134,6 +134,15 @@ __global__ void __launch_bounds__(kPutThreads) dispatch_put_kernel(const PutPara
     for (int rr = 0; rr < rows; ++rr) {
       const int flat = p.order[e.x + first + rr];
       const int token = flat / p.top_k;
+      // Index check (warp-uniform): a send-order entry outside the token range or a destination row outside the
+      // slice buffer is recorded and the row is skipped, never dereferenced. The arrival is still signalled, so
+      // nothing waits for the row; the recorded status tells the host that the pass is invalid.
+      if (flat < 0 || token >= p.num_tokens || e.z + first + rr >= S) {
+        if (lane == 0)
+          report_status(p.status, kStatusBadIndex, kKernelPut, 0, p.slice, e.x + first + rr,
+                        static_cast<uint32_t>(p.num_tokens), static_cast<uint32_t>(token));
+        continue;
+      }
       const size_t drow = static_cast<size_t>(buf) * S + e.z + first + rr;
       if (p.peer_xq == nullptr) {
         copy_row_bf16(p.x + static_cast<size_t>(token) * D, p.peer_x[r] + drow * D, D, lane);

@@ -16,6 +16,7 @@ struct PutParams {
   int slice;            // slice index inside the pass
   uint32_t seq;         // global slice sequence number (selects the double buffer, orders credits)
   int me, top_k, hidden;
+  int num_tokens;       // rows of x (and g): send-order entries are checked against it
   const int* order;                 // [T*K] flat assignment index t*K+k at each send-order position
   const __nv_bfloat16* x;           // [T, D] tokens (gathered by token id: no send-order copy exists)
   const __nv_bfloat16* g;           // [T, D] output gradient, or null in the forward

@@ -309,6 +309,7 @@ void FusedRank::put(int64_t j, torch::Tensor plan, torch::Tensor order, torch::T
   p.x = reinterpret_cast<const __nv_bfloat16*>(x.data_ptr());
   p.g = g.has_value() ? reinterpret_cast<const __nv_bfloat16*>(g->data_ptr()) : nullptr;
   p.w_flat = w_flat.data_ptr<float>();
+  p.num_tokens = static_cast<int>(x.size(0));
   p.peer_x = table<__nv_bfloat16>(kTabX);
   p.peer_g = table<__nv_bfloat16>(kTabG);
   p.peer_w = table<float>(kTabW);

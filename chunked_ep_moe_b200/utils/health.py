@@ -31,9 +31,10 @@ class PlanMismatch(RuntimeError):
 
 class RankHealth:
     def __init__(self, store, rank: int, world: int, prefix: str = "cem/health", timeout_s: float = 30.0,
-                 poll_s: float = 0.02):
+                 poll_s: float = 0.02, store_host: int = 0):
         self.store, self.rank, self.world = store, rank, world
         self.prefix, self.timeout_s, self.poll_s = prefix, timeout_s, poll_s
+        self.store_host = store_host  # the rank whose process serves the store: if the store dies, that rank is gone
 
     def _key(self, rank: int) -> str:
         return f"{self.prefix}/{rank}"
@@ -61,7 +62,14 @@ class RankHealth:
         missing = set(range(self.world)) - {self.rank}
         while missing:
             for r in list(missing):
-                s = self._peer_step(r)
+                try:
+                    s = self._peer_step(r)
+                except PeerFailure:
+                    raise
+                except Exception:  # noqa: BLE001 - the store itself stopped answering: its host has left
+                    if self.rank == self.store_host:
+                        raise
+                    raise PeerFailure(step, [self.store_host], time.monotonic() - start) from None
                 if s is not None and s >= step:
                     missing.discard(r)
                 elif s == -1:

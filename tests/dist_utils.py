@@ -29,6 +29,17 @@ def _worker(rank, world, port, fn, args, out_dir):
         torch.save({"ok": False, "error": traceback.format_exc()}, os.path.join(out_dir, f"{rank}.pt"))
         raise
     finally:
+        # Rank 0 hosts the c10d store: it must be the last to leave, or a slower rank's store call fails with a
+        # connection error that has nothing to do with what the test checks.
+        try:
+            store = dist.distributed_c10d._get_default_store()
+            store.add("cem/test/exited", 1)
+            if rank == 0:
+                deadline = time.monotonic() + 60.0
+                while int(store.add("cem/test/exited", 0)) < world and time.monotonic() < deadline:
+                    time.sleep(0.05)
+        except Exception:  # noqa: BLE001 - a dead store must not mask the test's own outcome
+            pass
         dist.destroy_process_group()
 
 

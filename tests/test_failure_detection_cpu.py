@@ -105,3 +105,23 @@ def test_collective_with_an_absent_peer_errors_out_instead_of_hanging():
     assert results[1] == "left"
     kind, waited, _ = results[0]
     assert kind == "error" and waited < 30.0
+
+
+class _DeadStore:
+    """A store whose server has gone away: every call fails the way a closed TCP store does."""
+
+    def set(self, key, value):
+        raise RuntimeError("Connection was likely closed")
+
+    def check(self, keys):
+        raise RuntimeError("Connection was likely closed")
+
+    def get(self, key):
+        raise RuntimeError("Connection was likely closed")
+
+
+def test_a_dead_store_names_the_rank_that_hosted_it():
+    health = RankHealth(_DeadStore(), rank=3, world=4, timeout_s=1.0)
+    with pytest.raises(PeerFailure) as info:
+        health.check_peers(5)
+    assert info.value.missing == [0] and info.value.step == 5

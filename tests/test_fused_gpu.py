@@ -153,6 +153,36 @@ def test_pipeline_counters_count_every_k_block():
     assert int(total[fused.GEMM_MODE_NAMES.index("tgmm"), slot["k_blocks"]]) == 0  # no backward ran
 
 
+def test_bad_send_order_entry_is_reported_not_dereferenced():
+    """A send-order entry outside the token range: the put kernel records it and skips the row (no wild read)."""
+    from chunked_ep_moe_b200.ops import fused
+
+    torch.manual_seed(0)
+    T, D, F, E, K, S = 64, 256, 256, 2, 2, 136  # a geometry no other test uses: the workspace is thrown away below
+    cfg = ChunkedMoEConfig(num_experts=E, top_k=K, slice_size=S, transport="nvshmem", expert_compute="fused",
+                           stripe_width=64)
+    ws = fused.get_workspace(cfg, None, D, F, T * K)
+    rank = ws.rank
+    x = torch.randn(T, D, device="cuda").bfloat16()
+    ids = torch.stack([torch.randperm(E, device="cuda")[:K] for _ in range(T)]).int().contiguous()
+    w_flat = torch.rand(T * K, device="cuda")
+    plan = torch.empty(ws.plan_ints, dtype=torch.int32, device="cuda")
+    order = torch.empty(T * K, dtype=torch.int32, device="cuda")
+    inv_order = torch.empty_like(order)
+    try:
+        n = rank.begin_forward(ids, plan, order, inv_order, ws.dummy_counts, False)
+        assert n == 1
+        order[5] = T * K + 7  # token index T + 3: past the end of x
+        rank.put(0, plan, order, x, None, w_flat)
+        torch.cuda.synchronize()
+        with pytest.raises(RuntimeError, match="index check failed"):
+            rank.check_status()
+        rank.check_status()  # the block was cleared: a second check is clean
+    finally:
+        torch.cuda.synchronize()
+        fused.release_workspaces()  # the pass was abandoned half way: do not reuse this workspace
+
+
 def test_fused_expert_compute_on_a_collective_transport():
     """`expert_compute="fused"` under `transport="ragged_a2a"`: the library exchange feeds the sm_100a kernels."""
     gen = torch.Generator().manual_seed(4)
