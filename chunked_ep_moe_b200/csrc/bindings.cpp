@@ -88,6 +88,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("arena_layout", &arena_layout_dict, "byte offsets inside one rank's symmetric arena");
   m.def("pair_grid_used", []() { return cem::g_pair_grid_used; }, "grid of the last CTA-pair GEMM launch");
   m.def("wait_probe", &wait_probe, "bounded-wait self test kernel");
+  m.def("format_status", &cem::format_status, "text of a recorded status block");
   py::class_<cem::FusedRank>(m, "FusedRank")
       .def(py::init<int, int, int, int, int, int, int, int, int, int, int, bool, int64_t, std::vector<int64_t>, bool,
                     int64_t, int, bool>(),

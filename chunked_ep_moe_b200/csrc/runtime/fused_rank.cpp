@@ -3,9 +3,9 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
-#include <sstream>
 #include <stdexcept>
 
 #include "tensor_map.h"
@@ -15,11 +15,7 @@ namespace cem {
 namespace {
 
 inline void cuda_check(cudaError_t err, const char* what) {
-  if (err != cudaSuccess) {
-    std::ostringstream os;
-    os << what << ": " << cudaGetErrorString(err);
-    throw std::runtime_error(os.str());
-  }
+  if (err != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(err));
 }
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -198,13 +194,24 @@ void FusedRank::check_status() {
   cuda_check(cudaStreamSynchronize(st), "status sync");
   const int32_t* s = host_header_ + 16;
   if (s[0] != 0) {
-    std::ostringstream os;
-    os << "chunked_moe fused path: " << status_name(s[0]) << " (code " << s[0] << ", kernel " << s[1] << ", mode "
-       << s[2] << ", slice/tile " << s[3] << ", detail " << s[4] << ", expected " << static_cast<uint32_t>(s[5])
-       << ", seen " << static_cast<uint32_t>(s[6]) << ", block " << s[7] << ", rank " << me_ << ")";
+    const std::string message = format_status(std::vector<int64_t>(s, s + 8), me_);
     cuda_check(cudaMemsetAsync(status_.data_ptr(), 0, 8 * sizeof(int32_t), st), "status clear");
-    throw std::runtime_error(os.str());
+    cuda_check(cudaStreamSynchronize(st), "status clear sync");
+    throw std::runtime_error(message);
   }
+}
+
+std::string format_status(const std::vector<int64_t>& s, int rank) {
+  if (s.size() < 8) return "chunked_moe fused path: malformed status block";
+  char buf[512];
+  std::snprintf(buf, sizeof(buf),
+                "chunked_moe fused path: %s (code %lld, kernel %lld, mode %lld, slice/tile %lld, detail %lld, "
+                "expected %llu, seen %llu, block %lld, rank %d)",
+                status_name(static_cast<int>(s[0])), static_cast<long long>(s[0]), static_cast<long long>(s[1]),
+                static_cast<long long>(s[2]), static_cast<long long>(s[3]), static_cast<long long>(s[4]),
+                static_cast<unsigned long long>(static_cast<uint32_t>(s[5])),
+                static_cast<unsigned long long>(static_cast<uint32_t>(s[6])), static_cast<long long>(s[7]), rank);
+  return std::string(buf);
 }
 
 void FusedRank::sort_only(torch::Tensor expert_ids, torch::Tensor order, torch::Tensor inv_order,

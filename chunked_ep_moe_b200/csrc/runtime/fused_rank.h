@@ -34,6 +34,9 @@ struct ArenaLayout {
 
 ArenaLayout make_arena_layout(int P, int L, int S, int D, int tk_cap, bool fp8);
 
+// Text of a recorded status block {code, kernel, mode, slice, detail, expected, seen, block} (what check_status raises).
+std::string format_status(const std::vector<int64_t>& status, int rank);
+
 class FusedRank {
  public:
   FusedRank(int P, int L, int me, int S, int D, int F, int K, int stripe, int tk_cap, int max_slices, int num_sms,

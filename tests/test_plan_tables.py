@@ -96,3 +96,15 @@ def test_tables_match_torch_planner(P, L, S, skew):
             present = set(gt[:, 0].tolist())
             assert present >= {e for e in range(L) if groups[e] > 0}
         np.testing.assert_array_equal(seen_final, np.ones(L))  # every expert's gradient is finalised exactly once
+
+
+def test_status_block_text():
+    """The message `check_status` raises for a recorded kernel error (formatting runs without a GPU)."""
+    from chunked_ep_moe_b200 import _build
+
+    ext = _build.load()
+    text = ext.format_status([5, 2, 0, 1, 5, 64, 67, 3], 2)
+    assert "index check failed" in text and "detail 5" in text and "expected 64" in text and "rank 2" in text
+    assert "pipeline barrier timed out" in ext.format_status([1, 1, 4, 17, 302, 0, 0, 9], 0)
+    assert "expected 4294967295" in ext.format_status([2, 1, 0, 0, 0, -1, 0, 0], 0)  # counters are unsigned
+    assert "malformed" in ext.format_status([1, 2], 0)
