@@ -57,13 +57,18 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
-// Bounded wait on an mbarrier phase: gives up (returns false) once `limit_us` microseconds have passed.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit_us) {
+// Bounded wait on an mbarrier phase: gives up (returns false) once `limit_us` microseconds have passed, or as soon
+// as `*abort` is set (another warp of the CTA has recorded an error and everybody is unwinding).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit_us,
+                                          const volatile int* abort = nullptr) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 0 && global_timer_ns() - t0 > static_cast<uint64_t>(limit_us) * 1000ull) return false;
+    if ((i & 63u) == 0) {
+      if (abort != nullptr && *abort != 0) return false;
+      if (global_timer_ns() - t0 > static_cast<uint64_t>(limit_us) * 1000ull) return false;
+    }
   }
 }
 

@@ -149,7 +149,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
           const long long w0 = counting ? clock64() : 0;
-          if (!mbar_wait(empty_bar(s), ph ^ 1u, p.mbar_limit)) {
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, p.mbar_limit, abort_flag)) {
             report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 100 + s, 0, 0);
             *abort_flag = 1;
             break;
@@ -211,7 +211,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
       const int solo_kblocks = ragged_tail ? tl.kblocks - 1 : tl.kblocks;
       if (lane == 0) {
         const long long w0 = counting ? clock64() : 0;
-        bool ok = mbar_wait(acc_empty_bar(as), aph ^ 1u, p.mbar_limit);
+        bool ok = mbar_wait(acc_empty_bar(as), aph ^ 1u, p.mbar_limit, abort_flag);
         if (counting) acc_wait += clock64() - w0;
         if (!ok) {
           report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 200 + as, 0, 0);
@@ -221,7 +221,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
         for (int kb = 0; ok && kb < solo_kblocks; ++kb) {
           const uint32_t i = it + kb;
           const long long w1 = counting ? clock64() : 0;
-          ok = mbar_wait(full_bar(i % kStages), (i / kStages) & 1u, p.mbar_limit);
+          ok = mbar_wait(full_bar(i % kStages), (i / kStages) & 1u, p.mbar_limit, abort_flag);
           if (counting) full_wait += clock64() - w1;
           if (!ok) {
             report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 300 + (i % kStages), 0, 0);
@@ -242,7 +242,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
           bool ok = true;
           if (lane == 0) {
             const long long w1 = counting ? clock64() : 0;
-            ok = mbar_wait(full_bar(s), (it / kStages) & 1u, p.mbar_limit);
+            ok = mbar_wait(full_bar(s), (it / kStages) & 1u, p.mbar_limit, abort_flag);
             if (counting) full_wait += clock64() - w1;
             if (!ok) {
               report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 300 + s, 0, 0);
@@ -309,7 +309,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
       const int as = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1u;
       const long long w0 = counting ? clock64() : 0;
-      bool ok = mbar_wait(acc_full_bar(as), aph, p.mbar_limit);
+      bool ok = mbar_wait(acc_full_bar(as), aph, p.mbar_limit, abort_flag);
       if (counting) epi_wait += clock64() - w0;
       if (!ok) {
         report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 400 + as, 0, 0);

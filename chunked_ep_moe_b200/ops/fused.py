@@ -64,7 +64,7 @@ class FusedWorkspace:
             stripe=cfg.stripe_width, tk_cap=tk_cap, max_slices=self.max_slices,
             num_sms=int(os.environ.get("CEM_GEMM_GRID", cfg.num_sms)), fp8=self.fp8,
             arena=self.arena.local, peer_arenas=self.arena.peers, use_comm_stream=True,
-            spin_limit=_DEFAULT_SPIN_LIMIT, put_blocks=int(os.environ.get("CEM_PUT_BLOCKS", _PUT_BLOCKS)),
+            spin_limit=int(os.environ.get("CEM_SPIN_LIMIT", _DEFAULT_SPIN_LIMIT)), put_blocks=int(os.environ.get("CEM_PUT_BLOCKS", _PUT_BLOCKS)),
             cta_pairs=os.environ.get("CEM_CTA_PAIRS", "0") != "0")
         self.plan_ints = self.rank.plan_ints()
         self.dummy_counts = torch.zeros(1, dtype=torch.int32, device="cuda")

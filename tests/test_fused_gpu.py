@@ -183,6 +183,40 @@ def test_bad_send_order_entry_is_reported_not_dereferenced():
         fused.release_workspaces()  # the pass was abandoned half way: do not reuse this workspace
 
 
+def test_gemm_whose_rows_never_arrive_gives_up_and_reports(monkeypatch):
+    """The real swiglu kernel waiting for rows nobody sends: its bounded wait runs out, every warp unwinds promptly
+    (the barrier waits watch the CTA's abort flag), later kernels of the pass return at once, the host raises."""
+    import time
+
+    from chunked_ep_moe_b200.ops import fused
+
+    torch.manual_seed(0)
+    T, D, F, E, K, S = 64, 256, 256, 2, 2, 144  # a geometry no other test uses: the workspace is thrown away below
+    cfg = ChunkedMoEConfig(num_experts=E, top_k=K, slice_size=S, transport="nvshmem", expert_compute="fused",
+                           stripe_width=64)
+    monkeypatch.setenv("CEM_SPIN_LIMIT", "2000")  # ~1 ms of polling instead of seconds
+    ws = fused.get_workspace(cfg, None, D, F, T * K)
+    rank = ws.rank
+    ids = torch.stack([torch.randperm(E, device="cuda")[:K] for _ in range(T)]).int().contiguous()
+    w_up = (torch.randn(E, D, 2 * F, device="cuda") * 0.05).bfloat16()
+    w_down = (torch.randn(E, F, D, device="cuda") * 0.05).bfloat16()
+    plan = torch.empty(ws.plan_ints, dtype=torch.int32, device="cuda")
+    order = torch.empty(T * K, dtype=torch.int32, device="cuda")
+    inv_order = torch.empty_like(order)
+    try:
+        assert rank.begin_forward(ids, plan, order, inv_order, ws.dummy_counts, False) == 1
+        t0 = time.monotonic()
+        rank.compute_forward(0, plan, w_up, w_down)  # no put was launched: the arrival counters never move
+        torch.cuda.synchronize()
+        assert time.monotonic() - t0 < 5.0, "unwinding must not wait for the barrier limits"
+        with pytest.raises(RuntimeError, match="dispatched rows never arrived"):
+            rank.check_status()
+        rank.check_status()
+    finally:
+        torch.cuda.synchronize()
+        fused.release_workspaces()
+
+
 def test_fused_expert_compute_on_a_collective_transport():
     """`expert_compute="fused"` under `transport="ragged_a2a"`: the library exchange feeds the sm_100a kernels."""
     gen = torch.Generator().manual_seed(4)
