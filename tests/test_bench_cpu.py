@@ -80,3 +80,16 @@ ptxas info    : Used 32 registers"""
     work = compile_report.work_report(8, 256, 8, 8192, 7168, 2048, 8192, False)
     assert abs(work["GEMM TFLOP per rank per step"] - 23.09) < 0.01
     assert work["kernel launches per step"] == 104
+
+
+def test_host_side_helpers_degrade_quietly():
+    """CPU affinity binding without NVML, and the trainer profile's kernel grouping."""
+    assert bench.bind_near_gpu(0).startswith("cpu affinity unchanged")
+    sys.path.insert(0, os.path.join(ROOT, "bench"))
+    import trainer_profile
+
+    assert trainer_profile.group_of("void cem::(anonymous namespace)::grouped_gemm_kernel<0>(...)") == "fused MoE kernels"
+    assert trainer_profile.group_of("nvjet_tst_256x256_64x4_2x2_2cta_v_bz_NNT") == "library GEMMs"
+    assert trainer_profile.group_of("cudnn_generated_fort_native_sdpa_sm100_flash_fprop_f16") == "attention"
+    assert trainer_profile.group_of("void at::native::vectorized_elementwise_kernel<8, ...>") == \\
+        "elementwise / reductions / softmax"
