@@ -91,5 +91,5 @@ def test_host_side_helpers_degrade_quietly():
     assert trainer_profile.group_of("void cem::(anonymous namespace)::grouped_gemm_kernel<0>(...)") == "fused MoE kernels"
     assert trainer_profile.group_of("nvjet_tst_256x256_64x4_2x2_2cta_v_bz_NNT") == "library GEMMs"
     assert trainer_profile.group_of("cudnn_generated_fort_native_sdpa_sm100_flash_fprop_f16") == "attention"
-    assert trainer_profile.group_of("void at::native::vectorized_elementwise_kernel<8, ...>") == \\
-        "elementwise / reductions / softmax"
+    glue = trainer_profile.group_of("void at::native::vectorized_elementwise_kernel<8, ...>")
+    assert glue == "elementwise / reductions / softmax"
