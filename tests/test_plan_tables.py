@@ -3,6 +3,8 @@
 import numpy as np
 import pytest
 import torch
+from hypothesis import given, settings
+from hypothesis import strategies as st
 
 from chunked_ep_moe_b200 import _build
 from chunked_ep_moe_b200.ops import plan as plan_lib
@@ -25,9 +27,20 @@ def _counts(P, L, tokens, top_k, skew, seed):
 @pytest.mark.parametrize("P,L,S", [(1, 4, 16), (2, 2, 4), (4, 2, 5), (8, 4, 24), (4, 8, 1000)])
 @pytest.mark.parametrize("skew", ["uniform", "all_one", "empty"])
 def test_tables_match_torch_planner(P, L, S, skew):
+    _check_tables(P, L, S, 16, 2, skew, seed=P * 100 + L)
+
+
+@settings(max_examples=40, deadline=None)
+@given(P=st.integers(1, 6), L=st.integers(1, 5), S=st.integers(1, 40), tokens=st.integers(1, 24),
+       top_k=st.integers(1, 3), skew=st.sampled_from(["uniform", "all_one", "empty"]), seed=st.integers(0, 10**6))
+def test_tables_match_torch_planner_fuzzed(P, L, S, tokens, top_k, skew, seed):
+    """Arbitrary small geometries: single rows, S = 1, slices longer than the whole stream, experts with nothing."""
+    _check_tables(P, L, S, tokens, min(top_k, P * L), skew, seed)
+
+
+def _check_tables(P, L, S, tokens, top_k, skew, seed):
     ext = _build.load()
-    tokens, top_k = 16, 2
-    ids, orders, counts = _counts(P, L, tokens, top_k, skew, seed=P * 100 + L)
+    ids, orders, counts = _counts(P, L, tokens, top_k, skew, seed=seed)
     max_slices = P * tokens * top_k // S + 2
     lay = ext.plan_layout(P, L, S, max_slices)
     n = P * L
