@@ -97,3 +97,37 @@ def test_stats_helpers():
     assert abs(rl["compute_ms"] - 16.87) < 0.05 and rl["roofline_ms"] == rl["compute_ms"]
     hs = stats.header_stats([3, 20, 24, 5, 0, 16] + [0] * 10, 8)
     assert hs["my_active_slices"] == 3 and hs["my_padding_rows"] == 4
+
+
+def _ep_step(rank, world, tokens):
+    """One forward/backward + gradient reduction of the decoder on `world` expert-parallel data-parallel ranks."""
+    from chunked_ep_moe_b200.train import reduce_gradients
+
+    cfg = _tiny_cfg(aux_loss_coef=0.0)
+    model = DeepSeekTiny(cfg)
+    model.init_weights(seed=11, rank=rank)
+    per = tokens.shape[0] // world
+    mine = tokens[rank * per:(rank + 1) * per]
+    ce, aux = model(mine[:, :-1], mine[:, 1:])
+    (ce + aux).backward()
+    reduce_gradients(model, world)
+    dense = {n: p.grad.clone() for n, p in model.named_parameters() if not (n.endswith("w_up") or n.endswith("w_down"))}
+    experts = {n: p.grad.clone() for n, p in model.named_parameters() if n.endswith("w_up") or n.endswith("w_down")}
+    return {"loss": float(ce.detach()), "dense": dense, "experts": experts}
+
+
+def test_two_ranks_give_the_gradients_of_one():
+    """Splitting the batch over two ranks that each own half of the experts changes nothing: the mean loss, the
+    (all-reduced) dense gradients and the concatenated expert gradients equal the single-rank step's."""
+    from dist_utils import run_ranks
+
+    tokens = torch.randint(0, 97, (4, 13), generator=torch.Generator().manual_seed(7))
+    one = _ep_step(0, 1, tokens)
+    two = run_ranks(_ep_step, 2, tokens, timeout=300)
+    assert abs(one["loss"] - (two[0]["loss"] + two[1]["loss"]) / 2) < 1e-5
+    for name, grad in one["dense"].items():
+        for r in range(2):
+            assert torch.allclose(two[r]["dense"][name], grad, rtol=1e-4, atol=1e-6), name
+    for name, grad in one["experts"].items():  # [4 experts, ...] on one rank; [2 experts, ...] on each of two
+        both = torch.cat([two[0]["experts"][name], two[1]["experts"][name]])
+        assert torch.allclose(both, grad, rtol=1e-4, atol=1e-6), name
