@@ -52,6 +52,8 @@ def parse_args():
 
 
 def reference_unavailable():
+    if int(os.environ.get("RANK", "0")) != 0:  # one line per job, also when launched once per GPU
+        return
     print(json.dumps({
         "impl": "reference",
         "unavailable": "the reference is a JAX package (hatchling build backend, jax>=0.11.1); neither hatchling nor "
