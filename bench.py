@@ -279,7 +279,8 @@ def main():
     stop.record()
     sync_all()
     ms = start.elapsed_time(stop) / args.steps
-    n_launch = (launches() - l0) // max(args.steps, 1)
+    total_launches = launches() - l0
+    n_launch = total_launches // max(args.steps, 1)
 
     e2e = None
     if not args.no_e2e:
@@ -368,7 +369,8 @@ def main():
                              % ((w_up.numel() + w_down.numel()) * 2 / 1e9)},
             "clocks": clocks,
             "e2e": e2e,
-            "gpu_launches": int(n_launch),
+            "gpu_launches": int(total_launches),  # this repo's kernels launched inside the timed region (all steps)
+            "gpu_launches_per_step": int(n_launch),
             "host": affinity_note,
             "local_only_ms_per_step": local_ms,
             "exposed_a2a_ms_per_step": (ms - local_ms) if local_ms is not None else (0.0 if world == 1 else None),
