@@ -95,6 +95,21 @@ __device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, ui
   }
 }
 
+// One lane of a fully converged warp (always the same one for the same mask). The rest of the warp keeps running
+// the same instruction stream, so loop counters and descriptors stay warp-uniform values; the issuing lane of a
+// tcgen05.mma / tcgen05.commit sequence must be the same every time, which the deterministic election guarantees.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ---------------------------------------------------------------------------------------------
 // fences
 // ---------------------------------------------------------------------------------------------
@@ -129,6 +144,25 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
+
+// ---------------------------------------------------------------------------------------------
+// Bulk stores: this CTA's shared memory -> global memory (local or a peer GPU's), tracked in the issuing thread's
+// bulk async-groups. Plain stores through the async proxy: no tensor map, no cluster delivery of any kind.
+// Both addresses 16-byte aligned, size a multiple of 16 bytes.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void bulk_store(unsigned long long gdst, uint32_t smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(gdst), "r"(smem_src), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+
+// Waits until this thread's committed bulk stores have READ their shared-memory source (it may be overwritten).
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
+// Waits until this thread's committed bulk stores have completed (their writes are done).
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------------
 // TMEM allocation (one warp, all 32 lanes)

@@ -68,6 +68,28 @@ __device__ __forceinline__ void resolve_source(const GemmParams& p, int g, int g
   }
 }
 
+// Dispatch consumer: waits until the rows of local expert `g` that belong to slices <= p.slice have arrived from every
+// source rank (lane s watches source s), then orders the async proxy behind what was observed, because the rows were
+// written through the generic proxy and TMA reads them next. Returns false on expiry (status recorded, abort set).
+__device__ __forceinline__ bool wait_expert_rows(const GemmParams& p, int g, int lane, volatile int* abort_flag) {
+  bool ok = true;
+  if (lane < p.lay.P) {
+    const int i = lane * p.lay.L + g;
+    const int through = plan_clip((p.slice + 1) * p.lay.S - p.plan[p.lay.off_in_start + i], 0,
+                                  p.plan[p.lay.off_in_size + i]);
+    const uint32_t target = p.pass_base[i] + static_cast<uint32_t>(through);
+    uint32_t seen = 0;
+    ok = spin_until_reached(p.arrive + i, target, p.spin_limit, &seen);
+    if (!ok) {
+      report_status(p.status, kStatusArrivalTimeout, kKernelGemm, kModeSwiglu, p.slice, i, target, seen);
+      *abort_flag = 1;
+    }
+  }
+  ok = __all_sync(0xffffffffu, ok);
+  if (ok) fence_proxy_async_all();
+  return ok;
+}
+
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
 
 // `col0`, `ncols` (weight-gradient mode only): the accumulator columns this warp is responsible for; that mode may
@@ -135,32 +157,37 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
     unsigned long long dst = 0;
     if (src >= 0)
       dst = reinterpret_cast<unsigned long long>(p.peer_rows[src] + static_cast<size_t>(pos) * p.ld0 + tl.n * kBlockN);
+    // Every lane stages its own row (two 128-column halves, 256 bytes each) and hands it to the async proxy as one
+    // bulk store to the source rank. Nothing here depends on another lane, and nobody waits for a remote store: the
+    // copy engine keeps the stores of consecutive tiles in flight while the warp goes on to the next accumulator.
+    uint8_t* my_row = stage_gen + lane * kStageRowPitch;
+    const uint32_t my_row_s = smem_u32(my_row);
 #pragma unroll 1
     for (int half = 0; half < 2; ++half) {
+      bulk_wait_read();  // my previous store has read this staging row
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 4; c += 2) {
+        uint32_t r2[32];
         tmem_ld_32x32(tacc + half * 128 + c * 32, r);
+        tmem_ld_32x32(tacc + half * 128 + c * 32 + 32, r2);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int lc = c * 4 + i;  // 16-byte chunk of this row inside the 128-column half
-          int4 v = make_int4(pack_bf16(__uint_as_float(r[8 * i]) * w, __uint_as_float(r[8 * i + 1]) * w),
-                             pack_bf16(__uint_as_float(r[8 * i + 2]) * w, __uint_as_float(r[8 * i + 3]) * w),
-                             pack_bf16(__uint_as_float(r[8 * i + 4]) * w, __uint_as_float(r[8 * i + 5]) * w),
-                             pack_bf16(__uint_as_float(r[8 * i + 6]) * w, __uint_as_float(r[8 * i + 7]) * w));
-          *reinterpret_cast<int4*>(stage_gen + lane * 256 + ((lc ^ (lane & 15)) << 4)) = v;
+          *reinterpret_cast<int4*>(my_row + (c * 4 + i) * 16) =
+              make_int4(pack_bf16(__uint_as_float(r[8 * i]) * w, __uint_as_float(r[8 * i + 1]) * w),
+                        pack_bf16(__uint_as_float(r[8 * i + 2]) * w, __uint_as_float(r[8 * i + 3]) * w),
+                        pack_bf16(__uint_as_float(r[8 * i + 4]) * w, __uint_as_float(r[8 * i + 5]) * w),
+                        pack_bf16(__uint_as_float(r[8 * i + 6]) * w, __uint_as_float(r[8 * i + 7]) * w));
+          *reinterpret_cast<int4*>(my_row + (c * 4 + 4 + i) * 16) =
+              make_int4(pack_bf16(__uint_as_float(r2[8 * i]) * w, __uint_as_float(r2[8 * i + 1]) * w),
+                        pack_bf16(__uint_as_float(r2[8 * i + 2]) * w, __uint_as_float(r2[8 * i + 3]) * w),
+                        pack_bf16(__uint_as_float(r2[8 * i + 4]) * w, __uint_as_float(r2[8 * i + 5]) * w),
+                        pack_bf16(__uint_as_float(r2[8 * i + 6]) * w, __uint_as_float(r2[8 * i + 7]) * w));
         }
       }
-      __syncwarp();
-      // Coalesced: 16 lanes cover one row's 256 bytes, two rows per instruction.
-#pragma unroll 4
-      for (int rr = 0; rr < 16; ++rr) {
-        const int rsel = rr * 2 + (lane >> 4), c16 = lane & 15;
-        const unsigned long long d = __shfl_sync(0xffffffffu, dst, rsel);
-        const int4 v = *reinterpret_cast<const int4*>(stage_gen + rsel * 256 + ((c16 ^ (rsel & 15)) << 4));
-        if (d != 0) *reinterpret_cast<int4*>(d + half * 256 + c16 * 16) = v;
-      }
-      __syncwarp();
+      fence_proxy_async_smem();
+      if (dst != 0) bulk_store(dst + half * 256, my_row_s, 256);
+      bulk_commit();
     }
     if constexpr (MODE == kModeDx) {
       if (tl.n == 0 && src >= 0) {
@@ -288,46 +315,43 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
       }
     };
     if (final) {
-      // bf16 gradient: transpose 64-column passes through the warp's staging buffer (32 rows x 128 bytes, 16-byte
-      // chunks XOR-swizzled by row) so every store instruction writes four full 128-byte row pieces instead of 32
-      // scattered 16-byte ones.
-      __nv_bfloat16* warp_out = p.grad_out + static_cast<size_t>(tl.g) * m_total * n_total +
-                                static_cast<size_t>(tl.m * kBlockM + q * 32) * n_total + tl.n * kBlockN;
-      auto stage_chunk = [&](int c, const uint32_t (&v)[32]) {  // c: 32-column chunk inside the pass (0 or 1)
+      // bf16 gradient: every lane stages 128 columns (256 bytes) of its own row and stores them with one bulk copy,
+      // so the gradient leaves in full lines through the async proxy and the warp never waits for a store.
+      __nv_bfloat16* my_out = p.grad_out + static_cast<size_t>(tl.g) * m_total * n_total + row_off;
+      uint8_t* my_row = stage_gen + lane * kStageRowPitch;
+      const uint32_t my_row_s = smem_u32(my_row);
+      auto stage_chunk = [&](int c, const uint32_t (&v)[32]) {  // c: 32-column chunk inside the 128-column piece
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int lc = c * 4 + i;
-          *reinterpret_cast<int4*>(stage_gen + lane * 128 + ((lc ^ (lane & 7)) << 4)) =
+        for (int i = 0; i < 4; ++i)
+          *reinterpret_cast<int4*>(my_row + (c * 4 + i) * 16) =
               make_int4(pack_bf16(__uint_as_float(v[8 * i]), __uint_as_float(v[8 * i + 1])),
                         pack_bf16(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3])),
                         pack_bf16(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5])),
                         pack_bf16(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7])));
-        }
       };
 #pragma unroll 1
-      for (int col = col0; col < col0 + ncols; col += 64) {
-        if (first && tl.kblocks > 0) {
-          // Common case (the expert lies inside one slice): two TMEM loads per wait.
-          uint32_t r2[32];
-          tmem_ld_32x32(tacc + col, r);
-          tmem_ld_32x32(tacc + col + 32, r2);
-          tmem_ld_wait();
-          stage_chunk(0, r);
-          stage_chunk(1, r2);
-        } else {
-          load_chunk(col);
-          stage_chunk(0, r);
-          load_chunk(col + 32);
-          stage_chunk(1, r);
+      for (int col = col0; col < col0 + ncols; col += 128) {
+        bulk_wait_read();  // my previous store has read this staging row
+#pragma unroll 1
+        for (int c = 0; c < 4; c += 2) {
+          if (first && tl.kblocks > 0) {
+            // Common case (the expert lies inside one slice): two TMEM loads per wait.
+            uint32_t r2[32];
+            tmem_ld_32x32(tacc + col + c * 32, r);
+            tmem_ld_32x32(tacc + col + c * 32 + 32, r2);
+            tmem_ld_wait();
+            stage_chunk(c, r);
+            stage_chunk(c + 1, r2);
+          } else {
+            load_chunk(col + c * 32);
+            stage_chunk(c, r);
+            load_chunk(col + c * 32 + 32);
+            stage_chunk(c + 1, r);
+          }
         }
-        __syncwarp();
-#pragma unroll
-        for (int rr = 0; rr < 8; ++rr) {
-          const int rsel = rr * 4 + (lane >> 3), c8 = lane & 7;
-          const int4 v = *reinterpret_cast<const int4*>(stage_gen + rsel * 128 + ((c8 ^ (rsel & 7)) << 4));
-          *reinterpret_cast<int4*>(warp_out + static_cast<size_t>(rsel) * n_total + col + c8 * 8) = v;
-        }
-        __syncwarp();
+        fence_proxy_async_smem();
+        bulk_store(reinterpret_cast<unsigned long long>(my_out + col), my_row_s, 256);
+        bulk_commit();
       }
     } else {
 #pragma unroll 1
@@ -343,9 +367,12 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
   }
 }
 
-// Releases this warp's returned-row counts to their source ranks: every lane's stores are ordered before the
-// warp barrier, lane s then fences at system scope and adds its count to source s's counter.
+// Releases this warp's returned-row counts to their source ranks: every lane first waits until its own bulk stores
+// have completed (the full wait, not the read-only one: the rows must have landed), the warp meets, and lane s then
+// fences at system scope and adds its count to source s's counter.
 __device__ __forceinline__ void flush_returned(const GemmParams& p, int lane, uint32_t returned) {
+  bulk_wait_all();
+  fence_proxy_async_all();
   __syncwarp();
   if (lane < p.lay.P && returned > 0) {
     __threadfence_system();

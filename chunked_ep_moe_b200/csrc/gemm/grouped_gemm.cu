@@ -3,8 +3,9 @@
 //   warp 0      TMA producer. Walks this CTA's tiles, (for the dispatch consumer) acquires the
 //               arrival counters of the tile's expert, then streams A/B k-blocks into a 4-stage
 //               shared-memory ring with cp.async.bulk.tensor (this CTA's shared memory only).
-//   warp 1      MMA issuer. One lane issues tcgen05.mma (128x256x16, bf16 -> fp32 in TMEM) and
-//               commits to the ring's empty barriers and to the accumulator-full barrier.
+//   warp 1      MMA issuer. The warp walks the k-blocks in step; one elected lane issues tcgen05.mma
+//               (128x256x16, bf16 -> fp32 in TMEM) and commits to the ring's empty barriers and to
+//               the accumulator-full barrier.
 //   warps 2-5   Epilogue. Each warp owns 32 TMEM lanes (= 32 tile rows, one row per thread),
 //               reads the accumulator with tcgen05.ld and applies the mode's fused epilogue.
 //
@@ -64,16 +65,19 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
   const uint32_t staging_base = smem_base + kStages * kStageBytes;
   uint8_t* staging_gen = smem_gen + kStages * kStageBytes;
   const uint32_t bar_base = staging_base + kStagingBytes;
-  // barriers: full[kStages], empty[kStages], acc_full[2], acc_empty[2], drain; then tmem slot, abort flag
+  // barriers: full[kStages], empty[kStages], acc_full[2], acc_empty[2], drain; then tmem slot, abort flag, early flag
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto acc_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
   auto acc_empty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + 2 + s); };
   const uint32_t drain_bar = bar_base + 8u * (2 * kStages + 4);
-  const uint32_t tmem_slot = bar_base + 8u * (2 * kStages + 5);
-  volatile uint32_t* tmem_slot_gen =
-      reinterpret_cast<volatile uint32_t*>(staging_gen + kStagingBytes + 8 * (2 * kStages + 5));
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(staging_gen + kStagingBytes + 8 * (2 * kStages + 5) + 4);
+  constexpr int kSlotOff = 8 * (2 * kStages + 5);
+  static_assert(kSlotOff + 12 <= kSmemTailBytes, "barrier area too small");
+  const uint32_t tmem_slot = bar_base + kSlotOff;
+  uint8_t* tail_gen = staging_gen + kStagingBytes;
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(tail_gen + kSlotOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail_gen + kSlotOff + 4);
+  volatile int* early_flag = reinterpret_cast<volatile int*>(tail_gen + kSlotOff + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool counting = p.prof != nullptr;
@@ -81,11 +85,16 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
     atomicAdd(p.prof + static_cast<size_t>(blockIdx.x) * kProfSlots + slot, static_cast<unsigned long long>(v));
   };
 
+  // The aligned layout must fit into what the launch provided (the slack covers a base that is not 1024-byte aligned).
+  if (smem_base - smem_u32(smem_raw) > static_cast<uint32_t>(kSmemAlignSlack)) {
+    if (threadIdx.x == 0) report_status(p.status, kStatusBadIndex, kKernelGemm, MODE, -1, 0, kSmemAlignSlack,
+                                        smem_base - smem_u32(smem_raw));
+    return;
+  }
   // An earlier kernel of this pass already gave up: do nothing, so the error reaches the host quickly.
-  __shared__ int s_early;
-  if (threadIdx.x == 0) s_early = (p.status != nullptr && p.status->code != 0) ? 1 : 0;
+  if (threadIdx.x == 0) *early_flag = (p.status != nullptr && p.status->code != 0) ? 1 : 0;
   __syncthreads();
-  if (s_early) return;
+  if (*early_flag) return;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -120,45 +129,39 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
     uint32_t it = 0;
     int waited_expert = -1;
     long long empty_wait = 0;
-    for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
-      const Tile tl = decode_tile<MODE>(p, t, num_entries);
-      if constexpr (MODE == kModeSwiglu) {
-        if (p.arrive != nullptr && tl.g != waited_expert) {
-          // Rows of expert g come from every source rank; lane s watches source s.
-          bool ok = true;
-          uint32_t seen = 0, target = 0;
-          if (lane < p.lay.P) {
-            const int i = lane * p.lay.L + tl.g;
-            const int through = plan_clip((p.slice + 1) * p.lay.S - p.plan[p.lay.off_in_start + i], 0,
-                                          p.plan[p.lay.off_in_size + i]);
-            target = p.pass_base[i] + static_cast<uint32_t>(through);
-            ok = spin_until_reached(p.arrive + i, target, p.spin_limit, &seen);
-            if (!ok) {
-              report_status(p.status, kStatusArrivalTimeout, kKernelGemm, MODE, p.slice, i, target, seen);
+    {
+      // The whole warp walks the k-blocks in step (every lane waits on the stage's barrier, one elected lane issues
+      // the copies), so stage index, phase and addresses stay warp-uniform values.
+      uint32_t ps = 0, pph = 0;
+      bool dead = false;
+      for (int t = blockIdx.x; t < num_tiles && !dead && !*abort_flag; t += gridDim.x) {
+        const Tile tl = decode_tile<MODE>(p, t, num_entries);
+        if constexpr (MODE == kModeSwiglu) {
+          if (p.arrive != nullptr && tl.g != waited_expert) {
+            if (!wait_expert_rows(p, tl.g, lane, abort_flag)) break;
+            waited_expert = tl.g;
+          }
+        }
+        for (int kb = 0; kb < tl.kblocks; ++kb) {
+          const long long w0 = counting ? clock64() : 0;
+          bool ok = mbar_wait(empty_bar(ps), pph ^ 1u, p.mbar_limit, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) {
+            if (lane == 0) {
+              report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 100 + ps, 0, 0);
               *abort_flag = 1;
             }
-          }
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          waited_expert = tl.g;
-          fence_proxy_async_all();  // arrived rows were written through the generic proxy; TMA reads them next
-        }
-      }
-      if (lane == 0) {
-        for (int kb = 0; kb < tl.kblocks; ++kb, ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1u;
-          const long long w0 = counting ? clock64() : 0;
-          if (!mbar_wait(empty_bar(s), ph ^ 1u, p.mbar_limit, abort_flag)) {
-            report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 100 + s, 0, 0);
-            *abort_flag = 1;
+            dead = true;
             break;
           }
           if (counting) empty_wait += clock64() - w0;
-          const uint32_t sa = smem_base + s * kStageBytes;
-          const uint32_t sb = sa + kStageBytesA;
-          mbar_expect_tx(full_bar(s), kStageBytes);
-          issue_kblock<MODE>(p, tl, kb, &map_a, &map_b, sa, sb, full_bar(s));
+          if (elect_one()) {
+            const uint32_t sa = smem_base + ps * kStageBytes;
+            mbar_expect_tx(full_bar(ps), kStageBytes);
+            issue_kblock<MODE>(p, tl, kb, &map_a, &map_b, sa, sa + kStageBytesA, full_bar(ps));
+          }
+          ++it;
+          if (++ps == kStages) { ps = 0; pph ^= 1u; }
         }
       }
       __syncwarp();
@@ -175,10 +178,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
     }
   } else if (warp == 1) {
     // ================================ MMA issuer ============================================
-    // ONE thread walks the k-blocks on its own: wait, fence, four MMAs, commit. Nothing in that loop involves the
-    // other lanes (a warp-wide vote and barrier per k-block cost ~400 of ~800 cycles per k-block and left the
-    // tensor pipe idle a third of the time); the warp only meets once per tile, and for the one weight-gradient
-    // k-block per tile whose rows past the group end must be zeroed by all lanes.
+    // All 32 lanes run the loop together (waits included) and ONE elected lane issues; loop counters, stage
+    // addresses and descriptors are then warp-uniform values. A loop run by a single lane inside a divergent branch
+    // cost ~610-780 cycles per k-block in this kernel and ~640-925 in the CTA-pair kernel; this form measures
+    // ~610-700 and ~520-630 (the tensor pipe's floor is 512).
     constexpr uint32_t idesc = make_instr_desc_bf16(kBlockM, kBlockN, Traits::kAMn, Traits::kBMn);
     constexpr uint32_t kDescStepA = Traits::kAMn ? 2048u : 32u;  // bytes per 16-wide k step inside a stage
     constexpr uint32_t kDescStepB = Traits::kBMn ? 2048u : 32u;
@@ -186,97 +189,93 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
     long long full_wait = 0, acc_wait = 0;
     const long long loop_c0 = counting ? clock64() : 0;
     const uint64_t loop_n0 = counting ? global_timer_ns() : 0;
-    // Issues `ksteps` MMAs of pipeline iteration `i` (lane 0 only) and frees the stage behind them.
-    auto issue_stage = [&](uint32_t i, uint32_t tmem_d, int ksteps, bool first_kblock) {
-      const uint32_t sa = smem_base + (i % kStages) * kStageBytes;
-      const uint64_t da = Traits::kAMn ? make_smem_desc(sa, 8192, 1024) : make_smem_desc(sa, 16, 1024);
-      const uint64_t db = Traits::kBMn ? make_smem_desc(sa + kStageBytesA, 8192, 1024)
-                                       : make_smem_desc(sa + kStageBytesA, 16, 1024);
+    {
+      // The whole warp walks the k-blocks in step: every lane waits on the stage's barrier, one elected lane (always
+      // the same one) issues the four MMAs and the commit. Stage index, phase and descriptors are warp-uniform values
+      // computed outside any divergent region.
+      uint32_t cs = 0, cph = 0;
+      bool dead = false;
+      auto issue_stage = [&](uint32_t s, uint32_t tmem_d, int ksteps, bool first_kblock) {
+        const uint32_t sa = smem_base + s * kStageBytes;
+        const uint64_t da = Traits::kAMn ? make_smem_desc(sa, 8192, 1024) : make_smem_desc(sa, 16, 1024);
+        const uint64_t db = Traits::kBMn ? make_smem_desc(sa + kStageBytesA, 8192, 1024)
+                                         : make_smem_desc(sa + kStageBytesA, 16, 1024);
+        if (elect_one()) {
 #pragma unroll
-      for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-        // The start address sits in the low 14 bits (16-byte units) and never carries out of them.
-        if (k < ksteps)
-          umma_bf16(tmem_d, da + ((k * kDescStepA) >> 4), db + ((k * kDescStepB) >> 4), idesc,
-                    (!first_kblock || k > 0) ? 1u : 0u);
-      }
-      umma_commit(empty_bar(i % kStages));
-    };
-    for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x, ++tcount) {
-      const Tile tl = decode_tile<MODE>(p, t, num_entries);
-      const int as = tcount & 1;
-      const uint32_t aph = (tcount >> 1) & 1u;
-      const uint32_t tmem_d = tmem_base + as * kBlockN;
-      // Weight gradients: the last k-block of a group may hold rows of the next group.
-      const bool ragged_tail = (MODE == kModeTgmm) && (tl.nrows % kBlockK) != 0;
-      const int solo_kblocks = ragged_tail ? tl.kblocks - 1 : tl.kblocks;
-      if (lane == 0) {
-        const long long w0 = counting ? clock64() : 0;
-        bool ok = mbar_wait(acc_empty_bar(as), aph ^ 1u, p.mbar_limit, abort_flag);
-        if (counting) acc_wait += clock64() - w0;
-        if (!ok) {
-          report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 200 + as, 0, 0);
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            // The start address sits in the low 14 bits (16-byte units) and never carries out of them.
+            if (k < ksteps)
+              umma_bf16(tmem_d, da + ((k * kDescStepA) >> 4), db + ((k * kDescStepB) >> 4), idesc,
+                        (!first_kblock || k > 0) ? 1u : 0u);
+          }
+          umma_commit(empty_bar(s));
+        }
+      };
+      auto fail = [&](int t, int detail) {
+        if (lane == 0) {
+          report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, detail, 0, 0);
           *abort_flag = 1;
         }
+        dead = true;
+      };
+      for (int t = blockIdx.x; t < num_tiles && !dead && !*abort_flag; t += gridDim.x, ++tcount) {
+        const Tile tl = decode_tile<MODE>(p, t, num_entries);
+        const int as = tcount & 1;
+        const uint32_t aph = (tcount >> 1) & 1u;
+        const uint32_t tmem_d = tmem_base + as * kBlockN;
+        // Weight gradients: the last k-block of a group may hold rows of the next group.
+        const bool ragged_tail = (MODE == kModeTgmm) && (tl.nrows % kBlockK) != 0;
+        const int solo_kblocks = ragged_tail ? tl.kblocks - 1 : tl.kblocks;
+        const long long w0 = counting ? clock64() : 0;
+        bool ok = __all_sync(0xffffffffu, mbar_wait(acc_empty_bar(as), aph ^ 1u, p.mbar_limit, abort_flag));
+        if (counting) acc_wait += clock64() - w0;
+        if (!ok) { fail(t, 200 + as); break; }
         tcgen05_fence_after_sync();
-        for (int kb = 0; ok && kb < solo_kblocks; ++kb) {
-          const uint32_t i = it + kb;
+        for (int kb = 0; kb < solo_kblocks; ++kb) {
           const long long w1 = counting ? clock64() : 0;
-          ok = mbar_wait(full_bar(i % kStages), (i / kStages) & 1u, p.mbar_limit, abort_flag);
+          ok = __all_sync(0xffffffffu, mbar_wait(full_bar(cs), cph, p.mbar_limit, abort_flag));
           if (counting) full_wait += clock64() - w1;
-          if (!ok) {
-            report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 300 + (i % kStages), 0, 0);
-            *abort_flag = 1;
-            break;
-          }
+          if (!ok) { fail(t, 300 + cs); break; }
           tcgen05_fence_after_sync();
-          issue_stage(i, tmem_d, kBlockK / kUmmaK, kb == 0);
-        }
-      }
-      __syncwarp();
-      if (*abort_flag) break;
-      it += solo_kblocks;
-      if constexpr (MODE == kModeTgmm) {
-        if (ragged_tail) {
-          const int kb = tl.kblocks - 1;
-          const int s = it % kStages;
-          bool ok = true;
-          if (lane == 0) {
-            const long long w1 = counting ? clock64() : 0;
-            ok = mbar_wait(full_bar(s), (it / kStages) & 1u, p.mbar_limit, abort_flag);
-            if (counting) full_wait += clock64() - w1;
-            if (!ok) {
-              report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 300 + s, 0, 0);
-              *abort_flag = 1;
-            }
-          }
-          ok = __shfl_sync(0xffffffffu, ok, 0);
-          if (!ok) break;
-          const int valid = tl.nrows - kb * kBlockK;  // rows of this k-block inside the group
-          const int ksteps = (valid + kUmmaK - 1) / kUmmaK;
-          // Rows [valid, ksteps*16) belong to the next group (or are padding): zero them in both operands.
-          // Each k row is one 128-byte line per 64-column chunk.
-          uint8_t* ga = smem_gen + s * kStageBytes;
-          const int zrows = ksteps * kUmmaK - valid;
-          // A k row is 48 16-byte pieces (6 chunks x 8): lane i clears piece i of chunks 0-3, lanes 0-15 also piece
-          // 32+i of chunks 4-5. Two stores per row, no index arithmetic in the loop.
-          uint8_t* lo = ga + (lane >> 3) * 8192 + (lane & 7) * 16 + valid * 128;
-          uint8_t* hi = lo + 4 * 8192;
-          for (int r = 0; r < zrows; ++r, lo += 128, hi += 128) {
-            *reinterpret_cast<int4*>(lo) = make_int4(0, 0, 0, 0);
-            if (lane < 16) *reinterpret_cast<int4*>(hi) = make_int4(0, 0, 0, 0);
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          tcgen05_fence_after_sync();
-          if (lane == 0) issue_stage(it, tmem_d, ksteps, kb == 0);
+          issue_stage(cs, tmem_d, kBlockK / kUmmaK, kb == 0);
           ++it;
+          if (++cs == kStages) { cs = 0; cph ^= 1u; }
         }
-      }
-      if (lane == 0) {
-        if (tl.kblocks > 0) {
-          umma_commit(acc_full_bar(as));
-        } else {
-          mbar_arrive(acc_full_bar(as));  // empty group: nothing was issued, the epilogue writes zeros
+        if (dead) break;
+        if constexpr (MODE == kModeTgmm) {
+          if (ragged_tail) {
+            const int kb = tl.kblocks - 1;
+            const long long w1 = counting ? clock64() : 0;
+            ok = __all_sync(0xffffffffu, mbar_wait(full_bar(cs), cph, p.mbar_limit, abort_flag));
+            if (counting) full_wait += clock64() - w1;
+            if (!ok) { fail(t, 300 + cs); break; }
+            const int valid = tl.nrows - kb * kBlockK;  // rows of this k-block inside the group
+            const int ksteps = (valid + kUmmaK - 1) / kUmmaK;
+            // Rows [valid, ksteps*16) belong to the next group (or are padding): zero them in both operands.
+            // A k row is one 128-byte line per 64-column chunk, 48 16-byte pieces in all (6 chunks x 8): lane i clears
+            // piece i of chunks 0-3, lanes 0-15 also piece 32+i of chunks 4-5.
+            uint8_t* ga = smem_gen + cs * kStageBytes;
+            const int zrows = ksteps * kUmmaK - valid;
+            uint8_t* lo = ga + (lane >> 3) * 8192 + (lane & 7) * 16 + valid * 128;
+            uint8_t* hi = lo + 4 * 8192;
+            for (int r = 0; r < zrows; ++r, lo += 128, hi += 128) {
+              *reinterpret_cast<int4*>(lo) = make_int4(0, 0, 0, 0);
+              if (lane < 16) *reinterpret_cast<int4*>(hi) = make_int4(0, 0, 0, 0);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            tcgen05_fence_after_sync();
+            issue_stage(cs, tmem_d, ksteps, kb == 0);
+            ++it;
+            if (++cs == kStages) { cs = 0; cph ^= 1u; }
+          }
+        }
+        if (elect_one()) {
+          if (tl.kblocks > 0) {
+            umma_commit(acc_full_bar(as));
+          } else {
+            mbar_arrive(acc_full_bar(as));  // empty group: nothing was issued, the epilogue writes zeros
+          }
         }
       }
       __syncwarp();
@@ -289,9 +288,11 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
       prof_add(kProfKBlocks, it);
       prof_add(kProfTiles, tcount);
     }
-    if (lane == 0 && *abort_flag) {
-      // Unwinding: let the MMAs already issued finish before TMEM is freed.
-      umma_commit(drain_bar);
+    if (*abort_flag) {
+      // Unwinding: let the MMAs already issued finish before TMEM is freed (the commit comes from the elected lane,
+      // which issued them).
+      __syncwarp();
+      if (elect_one()) umma_commit(drain_bar);
       mbar_wait(drain_bar, 0, p.mbar_limit);
     }
   } else {
@@ -327,6 +328,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
     }
     if (counting && ew == 0 && lane == 0) prof_add(kProfEpiWait, epi_wait);
     if constexpr (Traits::kCombine) flush_returned(p, lane, returned);  // also on the unwind path: what was stored is released
+    else bulk_wait_all();  // bulk stores of this thread still read the staging rows: no exit before they are done
   }
 
   // ================================ teardown ================================================
@@ -349,7 +351,7 @@ void launch_grouped_gemm(int mode, const GemmParams& p, const CUtensorMap& map_a
       cudaFuncSetAttribute(grouped_gemm_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes); \
       configured = true;                                                                                      \
     }                                                                                                         \
-    grouped_gemm_kernel<M><<<grid, 64 + 32 * epilogue_warps<M>(), kGemmSmemBytes, stream>>>(p, map_a, map_b);                  \
+    grouped_gemm_kernel<M><<<grid, 64 + 32 * epilogue_warps<M>(), kGemmSmemBytes, stream>>>(p, map_a, map_b);   \
     break;                                                                                                    \
   }
   switch (mode) {

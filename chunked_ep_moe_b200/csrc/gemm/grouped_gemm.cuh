@@ -83,8 +83,14 @@ struct GemmParams {
 constexpr int kStageBytesA = kBlockM * kBlockK * 2;
 constexpr int kStageBytesB = kBlockN * kBlockK * 2;
 constexpr int kStageBytes = kStageBytesA + kStageBytesB;
-constexpr int kStagingBytes = 4 * 32 * 256;  // per epilogue warp: 32 rows x 128 bf16 columns
-constexpr int kGemmSmemBytes = 1024 /*alignment slack*/ + kStages * kStageBytes + kStagingBytes + 256 /*barriers*/;
+// Epilogue staging, per epilogue warp: 32 rows x (256 bytes = 128 bf16 columns, + 16 bytes of padding so that the
+// 16-byte pieces eight neighbouring lanes write at the same column fall into eight different bank groups).
+constexpr int kStageRowPitch = 272;
+constexpr int kStagingBytes = 4 * 32 * kStageRowPitch;
+constexpr int kSmemAlignSlack = 512;  // the kernels check at run time that the 1024-byte aligned layout fits
+constexpr int kSmemTailBytes = 256;   // barriers, TMEM slot, flags
+constexpr int kGemmSmemBytes = kSmemAlignSlack + kStages * kStageBytes + kStagingBytes + kSmemTailBytes;
+static_assert(kGemmSmemBytes <= 232448, "more shared memory than one CTA can have");
 
 void launch_grouped_gemm(int mode, const GemmParams& p, const CUtensorMap& map_a, const CUtensorMap& map_b, int grid,
                          cudaStream_t stream);

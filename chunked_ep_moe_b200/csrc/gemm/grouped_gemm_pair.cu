@@ -101,10 +101,13 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
   auto acc_full_bar = [&](int s) { return bar_base + 8u * (3 * kPairStages + s); };
   auto acc_empty_bar = [&](int s) { return bar_base + 8u * (3 * kPairStages + 2 + s); };
   const uint32_t drain_bar = bar_base + 8u * (3 * kPairStages + 4);
-  const int slot_off = 8 * (3 * kPairStages + 5);
-  const uint32_t tmem_slot = bar_base + slot_off;
-  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(staging_gen + kStagingBytes + slot_off);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(staging_gen + kStagingBytes + slot_off + 4);
+  constexpr int kSlotOff = 8 * (3 * kPairStages + 5);
+  static_assert(kSlotOff + 12 <= kSmemTailBytes, "barrier area too small");
+  const uint32_t tmem_slot = bar_base + kSlotOff;
+  uint8_t* tail_gen = staging_gen + kStagingBytes;
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(tail_gen + kSlotOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail_gen + kSlotOff + 4);
+  volatile int* early_flag = reinterpret_cast<volatile int*>(tail_gen + kSlotOff + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = static_cast<int>(cluster_cta_rank());
@@ -114,15 +117,21 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
     atomicAdd(p.prof + static_cast<size_t>(blockIdx.x) * kProfSlots + slot, static_cast<unsigned long long>(v));
   };
 
+  // The aligned layout must fit into what the launch provided. Both CTAs of a pair see the same offsets, so they
+  // leave together.
+  if (smem_base - smem_u32(smem_raw) > static_cast<uint32_t>(kSmemAlignSlack)) {
+    if (threadIdx.x == 0) report_status(p.status, kStatusBadIndex, kKernelGemm, MODE, -1, 1, kSmemAlignSlack,
+                                        smem_base - smem_u32(smem_raw));
+    return;
+  }
   // An earlier kernel of this pass already gave up: both CTAs of the pair leave together (the leader decides).
-  __shared__ int s_early;
   if (threadIdx.x == 0 && leader) {
     const uint32_t v = (p.status != nullptr && p.status->code != 0) ? 1u : 0u;
-    s_early = static_cast<int>(v);
-    st_shared_cluster_u32(map_to_cta(smem_u32(&s_early), 1), v);
+    *early_flag = static_cast<int>(v);
+    st_shared_cluster_u32(map_to_cta(bar_base + kSlotOff + 8, 1), v);
   }
   cluster_sync_all();
-  if (s_early) return;
+  if (*early_flag) return;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; ++s) {
@@ -160,44 +169,38 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
     uint32_t it = 0;
     int waited_expert = -1;
     long long empty_wait = 0;
-    for (int t = first_tile; t < num_tiles && !*abort_flag; t += tile_step) {
-      const Tile tl = decode_pair_tile<MODE>(p, t, num_entries, rank);
-      if constexpr (MODE == kModeSwiglu) {
-        if (p.arrive != nullptr && tl.g != waited_expert) {
-          bool ok = true;
-          uint32_t seen = 0, target = 0;
-          if (lane < p.lay.P) {
-            const int i = lane * p.lay.L + tl.g;
-            const int through = plan_clip((p.slice + 1) * p.lay.S - p.plan[p.lay.off_in_start + i], 0,
-                                          p.plan[p.lay.off_in_size + i]);
-            target = p.pass_base[i] + static_cast<uint32_t>(through);
-            ok = spin_until_reached(p.arrive + i, target, p.spin_limit, &seen);
-            if (!ok) {
-              report_status(p.status, kStatusArrivalTimeout, kKernelGemm, MODE, p.slice, i, target, seen);
+    {
+      // The whole warp walks the k-blocks in step; one elected lane issues the copies.
+      uint32_t ps = 0, pph = 0;
+      bool dead = false;
+      for (int t = first_tile; t < num_tiles && !dead && !*abort_flag; t += tile_step) {
+        const Tile tl = decode_pair_tile<MODE>(p, t, num_entries, rank);
+        if constexpr (MODE == kModeSwiglu) {
+          if (p.arrive != nullptr && tl.g != waited_expert) {
+            if (!wait_expert_rows(p, tl.g, lane, abort_flag)) break;
+            waited_expert = tl.g;
+          }
+        }
+        for (int kb = 0; kb < tl.kblocks; ++kb) {
+          const long long w0 = counting ? clock64() : 0;
+          const bool ok = __all_sync(0xffffffffu, mbar_wait_poll(empty_bar(ps), pph ^ 1u, p.mbar_limit));
+          if (!ok) {
+            if (lane == 0) {
+              report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1100 + ps, 0, 0);
               *abort_flag = 1;
             }
-          }
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          waited_expert = tl.g;
-          fence_proxy_async_all();
-        }
-      }
-      if (lane == 0) {
-        for (int kb = 0; kb < tl.kblocks; ++kb, ++it) {
-          const int s = it % kPairStages;
-          const uint32_t ph = (it / kPairStages) & 1u;
-          const long long w0 = counting ? clock64() : 0;
-          if (!mbar_wait_poll(empty_bar(s), ph ^ 1u, p.mbar_limit)) {
-            report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1100 + s, 0, 0);
-            *abort_flag = 1;
+            dead = true;
             break;
           }
           if (counting) empty_wait += clock64() - w0;
-          const uint32_t sa = smem_base + s * kPairStageBytes;
-          const uint32_t fb = kRelay ? full_bar(s) : map_to_cta(full_bar(s), 0);
-          if (kRelay) mbar_expect_tx(fb, kPairStageBytes); else mbar_expect_tx_cluster(fb, kPairStageBytes);
-          issue_pair_kblock<MODE>(p, tl, kb, rank, &map_a, &map_b, sa, sa + kPairStageBytesA, fb);
+          if (elect_one()) {
+            const uint32_t sa = smem_base + ps * kPairStageBytes;
+            const uint32_t fb = kRelay ? full_bar(ps) : map_to_cta(full_bar(ps), 0);
+            if (kRelay) mbar_expect_tx(fb, kPairStageBytes); else mbar_expect_tx_cluster(fb, kPairStageBytes);
+            issue_pair_kblock<MODE>(p, tl, kb, rank, &map_a, &map_b, sa, sa + kPairStageBytesA, fb);
+          }
+          ++it;
+          if (++ps == kPairStages) { ps = 0; pph ^= 1u; }
         }
       }
       __syncwarp();
@@ -213,8 +216,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
     }
   } else if (warp == 1) {
     // ================================ MMA issuer (leader) / stage relay (peer) ==============
-    // As in the single-CTA kernel, ONE thread walks the k-blocks on its own; the warp meets once per tile and for
-    // the one weight-gradient k-block per tile whose rows past the group end are zeroed by all lanes.
+    // As in the single-CTA kernel, the whole warp walks the k-blocks in step and one elected lane issues.
     constexpr uint32_t idesc = make_instr_desc_bf16(2 * kBlockM, kBlockN, Traits::kAMn, Traits::kBMn);
     constexpr uint32_t kDescStepA = Traits::kAMn ? 2048u : 32u;
     constexpr uint32_t kDescStepB = Traits::kBMn ? 2048u : 32u;
@@ -223,113 +225,100 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
     long long full_wait = 0, acc_wait = 0;
     const long long loop_c0 = counting ? clock64() : 0;
     const uint64_t loop_n0 = counting ? global_timer_ns() : 0;
-    // Leader, lane 0: the pair MMAs of pipeline iteration `i`, then the stage is free in BOTH CTAs.
-    auto issue_stage = [&](uint32_t i, uint32_t tmem_d, int ksteps, bool first_kblock) {
-      const int s = i % kPairStages;
-      const uint32_t sa = smem_base + s * kPairStageBytes;
-      const uint64_t da = Traits::kAMn ? make_smem_desc(sa, 8192, 1024) : make_smem_desc(sa, 16, 1024);
-      const uint64_t db = Traits::kBMn ? make_smem_desc(sa + kPairStageBytesA, 8192, 1024)
-                                       : make_smem_desc(sa + kPairStageBytesA, 16, 1024);
+    {
+      // The whole warp walks the k-blocks in step; one elected lane (always the same one) issues MMAs and commits.
+      uint32_t cs = 0, cph = 0;
+      bool dead = false;
+      auto issue_stage = [&](uint32_t s, uint32_t tmem_d, int ksteps, bool first_kblock) {
+        const uint32_t sa = smem_base + s * kPairStageBytes;
+        const uint64_t da = Traits::kAMn ? make_smem_desc(sa, 8192, 1024) : make_smem_desc(sa, 16, 1024);
+        const uint64_t db = Traits::kBMn ? make_smem_desc(sa + kPairStageBytesA, 8192, 1024)
+                                         : make_smem_desc(sa + kPairStageBytesA, 16, 1024);
+        if (elect_one()) {
 #pragma unroll
-      for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-        if (k < ksteps)
-          umma_bf16_pair(tmem_d, da + ((k * kDescStepA) >> 4), db + ((k * kDescStepB) >> 4), idesc,
-                         (!first_kblock || k > 0) ? 1u : 0u);
-      }
-      umma_commit_pair_both(empty_bar(s));
-    };
-    for (int t = first_tile; t < num_tiles && !*abort_flag && (kRelay || leader); t += tile_step, ++tcount) {
-      const Tile tl = decode_pair_tile<MODE>(p, t, num_entries, rank);
-      const int as = tcount & 1;
-      const uint32_t aph = (tcount >> 1) & 1u;
-      const uint32_t tmem_d = tmem_base + as * kBlockN;
-      const bool ragged_tail = kRelay && (tl.nrows % kBlockK) != 0;
-      const int solo_kblocks = ragged_tail ? tl.kblocks - 1 : tl.kblocks;
-      if (lane == 0) {
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            if (k < ksteps)
+              umma_bf16_pair(tmem_d, da + ((k * kDescStepA) >> 4), db + ((k * kDescStepB) >> 4), idesc,
+                             (!first_kblock || k > 0) ? 1u : 0u);
+          }
+          umma_commit_pair_both(empty_bar(s));
+        }
+      };
+      auto fail = [&](int t, int detail) {
+        if (lane == 0) {
+          report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, detail, 0, 0);
+          *abort_flag = 1;
+        }
+        dead = true;
+      };
+      auto advance = [&]() {
+        ++it;
+        if (++cs == kPairStages) { cs = 0; cph ^= 1u; }
+      };
+      for (int t = first_tile; t < num_tiles && !dead && !*abort_flag && (kRelay || leader); t += tile_step, ++tcount) {
+        const Tile tl = decode_pair_tile<MODE>(p, t, num_entries, rank);
+        const int as = tcount & 1;
+        const uint32_t aph = (tcount >> 1) & 1u;
+        const uint32_t tmem_d = tmem_base + as * kBlockN;
+        const bool ragged_tail = kRelay && (tl.nrows % kBlockK) != 0;
+        const int solo_kblocks = ragged_tail ? tl.kblocks - 1 : tl.kblocks;
         bool ok = true;
         if (leader) {
           const long long w0 = counting ? clock64() : 0;
-          ok = mbar_wait_poll(acc_empty_bar(as), aph ^ 1u, p.mbar_limit);
+          ok = __all_sync(0xffffffffu, mbar_wait_poll(acc_empty_bar(as), aph ^ 1u, p.mbar_limit));
           if (counting) acc_wait += clock64() - w0;
-          if (!ok) {
-            report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1200 + as, 0, 0);
-            *abort_flag = 1;
-          }
+          if (!ok) { fail(t, 1200 + as); break; }
           tcgen05_fence_after_sync();
         }
-        for (int kb = 0; ok && kb < solo_kblocks; ++kb) {
-          const uint32_t i = it + kb;
-          const int s = i % kPairStages;
-          const uint32_t ph = (i / kPairStages) & 1u;
+        for (int kb = 0; kb < solo_kblocks; ++kb) {
           const long long w1 = counting ? clock64() : 0;
-          ok = mbar_wait(full_bar(s), ph, p.mbar_limit);
-          if (ok && kRelay && leader) ok = mbar_wait_poll(ready_bar(s), ph, p.mbar_limit);
+          ok = mbar_wait(full_bar(cs), cph, p.mbar_limit);
+          if (ok && kRelay && leader) ok = mbar_wait_poll(ready_bar(cs), cph, p.mbar_limit);
+          ok = __all_sync(0xffffffffu, ok);
           if (counting) full_wait += clock64() - w1;
-          if (!ok) {
-            report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1300 + s, 0, 0);
-            *abort_flag = 1;
-            break;
-          }
+          if (!ok) { fail(t, 1300 + cs); break; }
           if (!leader) {
-            mbar_arrive_cluster(map_to_cta(ready_bar(s), peer));  // this CTA's half of the stage is in place
-            continue;
-          }
-          tcgen05_fence_after_sync();
-          issue_stage(i, tmem_d, kBlockK / kUmmaK, kb == 0);
-        }
-      }
-      __syncwarp();
-      if (*abort_flag) break;
-      it += solo_kblocks;
-      if constexpr (kRelay) {
-        if (ragged_tail) {
-          const int kb = tl.kblocks - 1;
-          const int s = it % kPairStages;
-          const uint32_t ph = (it / kPairStages) & 1u;
-          bool ok = true;
-          if (lane == 0) {
-            ok = mbar_wait(full_bar(s), ph, p.mbar_limit);
-            if (!ok) {
-              report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1300 + s, 0, 0);
-              *abort_flag = 1;
-            }
-          }
-          ok = __shfl_sync(0xffffffffu, ok, 0);
-          if (!ok) break;
-          const int valid = tl.nrows - kb * kBlockK;
-          const int ksteps = (valid + kUmmaK - 1) / kUmmaK;
-          // Zero this CTA's rows [valid, ksteps*16) in its four 64-column chunks (2 of A, 2 of B).
-          uint8_t* ga = smem_gen + s * kPairStageBytes;
-          const int zrows = ksteps * kUmmaK - valid;
-          // A k row is 32 16-byte pieces here (4 chunks x 8): lane i clears piece i, one store per row.
-          uint8_t* piece = ga + (lane >> 3) * 8192 + (lane & 7) * 16 + valid * 128;
-          for (int r = 0; r < zrows; ++r, piece += 128) *reinterpret_cast<int4*>(piece) = make_int4(0, 0, 0, 0);
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (!leader) {
-            if (lane == 0) mbar_arrive_cluster(map_to_cta(ready_bar(s), peer));
+            if (elect_one()) mbar_arrive_cluster(map_to_cta(ready_bar(cs), peer));  // this CTA's half is in place
           } else {
-            if (lane == 0) {
-              ok = mbar_wait_poll(ready_bar(s), ph, p.mbar_limit);
-              if (!ok) {
-                report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1400 + s, 0, 0);
-                *abort_flag = 1;
-              }
-            }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) break;
             tcgen05_fence_after_sync();
-            if (lane == 0) issue_stage(it, tmem_d, ksteps, kb == 0);
+            issue_stage(cs, tmem_d, kBlockK / kUmmaK, kb == 0);
           }
-          ++it;
+          advance();
         }
-      }
-      if (leader && lane == 0) {
-        if (tl.kblocks > 0) {
-          umma_commit_pair_both(acc_full_bar(as));
-        } else {
-          mbar_arrive(acc_full_bar(as));  // empty group: both epilogues write zeros
-          mbar_arrive_cluster(map_to_cta(acc_full_bar(as), peer));
+        if (dead) break;
+        if constexpr (kRelay) {
+          if (ragged_tail) {
+            const int kb = tl.kblocks - 1;
+            ok = __all_sync(0xffffffffu, mbar_wait(full_bar(cs), cph, p.mbar_limit));
+            if (!ok) { fail(t, 1300 + cs); break; }
+            const int valid = tl.nrows - kb * kBlockK;
+            const int ksteps = (valid + kUmmaK - 1) / kUmmaK;
+            // Zero this CTA's rows [valid, ksteps*16) in its four 64-column chunks (2 of A, 2 of B): a k row is 32
+            // 16-byte pieces here, lane i clears piece i.
+            uint8_t* ga = smem_gen + cs * kPairStageBytes;
+            const int zrows = ksteps * kUmmaK - valid;
+            uint8_t* piece = ga + (lane >> 3) * 8192 + (lane & 7) * 16 + valid * 128;
+            for (int r = 0; r < zrows; ++r, piece += 128) *reinterpret_cast<int4*>(piece) = make_int4(0, 0, 0, 0);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (!leader) {
+              if (elect_one()) mbar_arrive_cluster(map_to_cta(ready_bar(cs), peer));
+            } else {
+              ok = __all_sync(0xffffffffu, mbar_wait_poll(ready_bar(cs), cph, p.mbar_limit));
+              if (!ok) { fail(t, 1400 + cs); break; }
+              tcgen05_fence_after_sync();
+              issue_stage(cs, tmem_d, ksteps, kb == 0);
+            }
+            advance();
+          }
+        }
+        if (leader && elect_one()) {
+          if (tl.kblocks > 0) {
+            umma_commit_pair_both(acc_full_bar(as));
+          } else {
+            mbar_arrive(acc_full_bar(as));  // empty group: both epilogues write zeros
+            mbar_arrive_cluster(map_to_cta(acc_full_bar(as), peer));
+          }
         }
       }
       __syncwarp();
@@ -342,14 +331,15 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
       prof_add(kProfKBlocks, it);
       prof_add(kProfTiles, tcount);
     }
-    if (leader && lane == 0 && *abort_flag) {
-      umma_commit_pair(drain_bar);
+    if (leader && *abort_flag) {
+      __syncwarp();
+      if (elect_one()) umma_commit_pair(drain_bar);
       mbar_wait(drain_bar, 0, p.mbar_limit);
     }
   } else {
     // ================================ epilogue (both CTAs) ==================================
     const int q = warp & 3;
-    uint8_t* stage_gen = staging_gen + (warp - 2) * 8192;
+    uint8_t* stage_gen = staging_gen + (warp - 2) * (kStagingBytes / 4);
     const uint32_t leader_acc_empty0 = map_to_cta(acc_empty_bar(0), 0);
     uint32_t tcount = 0, returned = 0;
     for (int t = first_tile; t < num_tiles && !*abort_flag; t += tile_step, ++tcount) {
@@ -371,6 +361,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
       if (lane == 0) mbar_arrive_cluster(leader_acc_empty0 + 8u * as);
     }
     if constexpr (Traits::kCombine) flush_returned(p, lane, returned);  // also on the unwind path: what was stored is released
+    else bulk_wait_all();  // bulk stores of this thread still read the staging rows: no exit before they are done
   }
 
   // ================================ teardown ================================================

@@ -39,6 +39,19 @@ _workspaces: dict = {}
 SOLO = "solo"
 
 
+def use_cta_pairs(tokens_times_k: int, local_experts: int) -> bool:
+    """Which GEMM kernel family a workspace runs: CTA pairs (`cta_group::2`, 256-row tiles) or single CTAs.
+
+    The pair kernels are faster per tile but round every expert's rows in a slice up to 256 instead of 128, so they
+    win once an expert receives many rows per pass (measured cross-over: ~512 rows per expert is a draw, 1024 rows
+    +5 %, 2048 rows +8 %). `CEM_CTA_PAIRS=0/1` overrides the choice.
+    """
+    env = os.environ.get("CEM_CTA_PAIRS")
+    if env is not None:
+        return env != "0"
+    return tokens_times_k // max(local_experts, 1) >= 768
+
+
 class FusedWorkspace:
     """Symmetric arena + per-rank executor for one (geometry, process group)."""
 
@@ -65,7 +78,7 @@ class FusedWorkspace:
             num_sms=int(os.environ.get("CEM_GEMM_GRID", cfg.num_sms)), fp8=self.fp8,
             arena=self.arena.local, peer_arenas=self.arena.peers, use_comm_stream=True,
             spin_limit=int(os.environ.get("CEM_SPIN_LIMIT", _DEFAULT_SPIN_LIMIT)), put_blocks=int(os.environ.get("CEM_PUT_BLOCKS", _PUT_BLOCKS)),
-            cta_pairs=os.environ.get("CEM_CTA_PAIRS", "0") != "0")
+            cta_pairs=use_cta_pairs(tk_cap, self.local_experts))
         self.plan_ints = self.rank.plan_ints()
         self.dummy_counts = torch.zeros(1, dtype=torch.int32, device="cuda")
 
