@@ -48,6 +48,10 @@ def parse_args():
     ap.add_argument("--slice-size", type=int, default=None)
     ap.add_argument("--skew", default="none", choices=["none", "zipf", "expert0"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-check", action="store_true", help="skip the sampled fp32 check of one step")
+    ap.add_argument("--no-baseline", action="store_true",
+                    help="skip timing the NCCL + library grouped-GEMM layer on the same tensors (fills vs_baseline)")
+    ap.add_argument("--baseline-steps", type=int, default=2)
     return ap.parse_args()
 
 
@@ -268,6 +272,19 @@ def main():
         step(x_d.clone(), ids_d, weights_d.clone())
     sync_all()
 
+    # One step at the benchmarked size against a sampled fp32 oracle (outside every timed region): 64 tokens per rank
+    # (output, dX, router-weight gradients) and both weight gradients of each rank's first and last expert.
+    check = None
+    if not args.no_check:
+        from chunked_ep_moe_b200.utils.verify import sampled_check
+
+        out_c, dx_c, dwt_c = step(x_d.clone(), ids_d, weights_d.clone())
+        check = sampled_check(x_d, ids_d, weights_d, g_d, w_up.detach(), w_down.detach(), out_c.detach(), dx_c, dwt_c,
+                              w_up.grad, w_down.grad, stripe=c["stripe"], group=group,
+                              tol=8e-2 if args.comm_dtype else 3e-2)
+        del out_c, dx_c, dwt_c
+        sync_all()
+
     sampler = ClockSampler(local_rank)
     sampler.start()
     l0 = launches()
@@ -326,10 +343,47 @@ def main():
         sync_all()
         local_ms = s0.elapsed_time(s1) / args.steps
 
-    t = torch.tensor([ms, e2e_ms if not args.no_e2e else 0.0, local_ms or 0.0], device=dev, dtype=torch.float64)
+    # Comparison arm in the same process, on the same tensors: the same layer on NCCL `all_to_all_single` + the
+    # library grouped GEMM (`transport="ragged_a2a"`, `expert_compute="reference"`), timed the same way.
+    base_ms, base_note = None, None
+    if fused and not args.no_baseline:
+        cfg_base = ChunkedMoEConfig(num_experts=E, top_k=K, slice_size=S, stripe_width=c["stripe"],
+                                    transport="ragged_a2a", expert_compute="reference", comm_dtype=args.comm_dtype)
+
+        def step_base():
+            x = x_d.detach().requires_grad_(True)
+            w = weights_d.detach().requires_grad_(True)
+            w_up.grad = None
+            w_down.grad = None
+            chunked_moe(x, ids_d, w, w_up, w_down, cfg_base, group).backward(g_d)
+
+        try:
+            w_up.grad = None
+            w_down.grad = None
+            torch.cuda.empty_cache()
+            step_base()
+            sync_all()
+            b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            b0.record()
+            for _ in range(args.baseline_steps):
+                step_base()
+            b1.record()
+            sync_all()
+            base_ms = b0.elapsed_time(b1) / args.baseline_steps
+        except Exception as exc:  # noqa: BLE001 - the headline number must survive a failing comparison arm
+            base_note = f"{type(exc).__name__}: {exc}"[:200]
+            base_ms = None
+        w_up.grad = None
+        w_down.grad = None
+
+    failed = torch.tensor([1.0 if base_ms is None else 0.0], device=dev, dtype=torch.float64)
+    t = torch.tensor([ms, e2e_ms if not args.no_e2e else 0.0, local_ms or 0.0, base_ms or 0.0], device=dev,
+                     dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        dist.all_reduce(failed, op=dist.ReduceOp.MAX, group=group)
     ms, e2e_ms, local_ms = float(t[0]), float(t[1]), (float(t[2]) if local_ms is not None else None)
+    base_ms = float(t[3]) if float(failed[0]) == 0.0 else None
     if not args.no_e2e:
         h2d = x_h.numel() * 2 + ids_h.numel() * 4 + weights_h.numel() * 4
         e2e = {"value": world * T / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
@@ -353,7 +407,9 @@ def main():
             "ms_per_step": ms,
             "higher_is_better": True,
             "scaling": "weak",
-            "vs_baseline": None,
+            # No published number exists for this metric (the reference was never run on a GPU), so the ratio is
+            # against the in-repo NCCL + library grouped-GEMM layer timed in this same process (`baseline` below).
+            "vs_baseline": (base_ms / ms) if base_ms else None,
             "dtype": "bf16",
             "data": "synthetic (seeded N(0,1) tokens, random-init N(0,%g) weights, top-%d of sigmoid logits)" % (c["std"], K),
             "impl": args.impl,
@@ -368,6 +424,11 @@ def main():
                        "l2": "inputs larger than L2: %.1f GB of expert weights stream through every step"
                              % ((w_up.numel() + w_down.numel()) * 2 / 1e9)},
             "clocks": clocks,
+            "check": check,
+            "baseline": ({"impl": "same layer on NCCL all_to_all_single + torch grouped_mm, same process and tensors",
+                          "ms_per_step": base_ms, "steps": args.baseline_steps, "warmup": 1,
+                          "value": world * T / (base_ms / 1e3)} if base_ms else
+                         ({"unavailable": base_note or "not run"} if fused else None)),
             "e2e": e2e,
             "gpu_launches": int(total_launches),  # this repo's kernels launched inside the timed region (all steps)
             "gpu_launches_per_step": int(n_launch),
@@ -382,6 +443,8 @@ def main():
 
         fused_mod.release_workspaces()
         dist.destroy_process_group()
+    if check is not None and not check["ok"]:
+        raise SystemExit(f"sampled fp32 check failed: {check}")
 
 
 if __name__ == "__main__":

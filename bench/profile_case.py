@@ -1,5 +1,9 @@
 """Small single-GPU case for kernel profiling: two forward+backward passes of the fused layer.
 
+Default: 16 experts, D=2048, F=1024, 16384 token copies. `--experts 16 --tokens 512 --top-k 8 --hidden 7168
+--ffn 2048` gives the weight-gradient shape of the 256-experts-per-GPU layout (256 rows per expert, 1.4 GB of
+weights) in one slice.
+
 Sized so that a full-section profiler capture of a few launches ends in about a minute: 16 experts,
 D=2048, F=1024 (201 MB of bf16 expert weights, larger than the 126 MB L2), 16384 token copies in
 two 8192-row slices. Launch order of one pass: forward = sort x3, plan, pass_begin, put, put,
@@ -9,6 +13,7 @@ two 8192-row slices. Launch order of one pass: forward = sort x3, plan, pass_beg
     python bench/profile_case.py            # prints per-pass device times
 """
 
+import argparse
 import math
 import os
 import sys
@@ -21,9 +26,17 @@ from chunked_ep_moe_b200 import ChunkedMoEConfig, chunked_moe  # noqa: E402
 
 
 def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--experts", type=int, default=16)
+    ap.add_argument("--top-k", type=int, default=4)
+    ap.add_argument("--hidden", type=int, default=2048)
+    ap.add_argument("--ffn", type=int, default=1024)
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--slice-size", type=int, default=8192)
+    args = ap.parse_args()
     torch.manual_seed(0)
     dev = torch.device("cuda:0")
-    E, K, D, F, T, S = 16, 4, 2048, 1024, 4096, 8192
+    E, K, D, F, T, S = args.experts, args.top_k, args.hidden, args.ffn, args.tokens, args.slice_size
     cfg = ChunkedMoEConfig(num_experts=E, top_k=K, slice_size=S, transport="nvshmem", expert_compute="fused",
                            stripe_width=64)
     x = torch.randn(T, D, device=dev, dtype=torch.bfloat16, requires_grad=True)

@@ -22,6 +22,7 @@ _SOURCES = [
     "bindings.cpp",
     "runtime/tensor_map.cpp",
     "runtime/fused_rank.cpp",
+    "runtime/kernel_runner.cpp",
     "gemm/grouped_gemm.cu",
     "gemm/grouped_gemm_pair.cu",
     "comm/comm_kernels.cu",

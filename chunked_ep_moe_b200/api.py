@@ -17,11 +17,15 @@ Only the inputs and the integer routing plan are saved between the passes.
 
 Backend selection: `transport="nvshmem"` + `expert_compute="fused"` runs the
 fused sm_100a executor; every other combination runs the torch slice loops on
-a collective transport.
+a collective transport. Shapes the kernels do not cover (D or F not a multiple
+of 256, other stripe widths, non-bf16 tensors) fall back to the collective
+path with a warning.
 """
 
 from __future__ import annotations
 
+import dataclasses
+import warnings
 from typing import Optional
 
 import torch
@@ -39,7 +43,7 @@ class _ChunkedMoECollective(torch.autograd.Function):
     def forward(ctx, x, expert_ids, weights, w_up, w_down, cfg, group):
         exchange = exchange_fn(cfg.transport)
         with torch.no_grad():
-            out, plan = layer_torch.forward_loop(x, expert_ids, weights, w_up, w_down, cfg, group, exchange)
+            out, plan = layer_torch.forward_pass(x, expert_ids, weights, w_up, w_down, cfg, group, exchange)
         ctx.save_for_backward(x, weights, w_up, w_down)
         ctx.plan, ctx.cfg, ctx.group = plan, cfg, group
         ctx.mark_non_differentiable(expert_ids)
@@ -50,7 +54,7 @@ class _ChunkedMoECollective(torch.autograd.Function):
         x, weights, w_up, w_down = ctx.saved_tensors
         exchange = exchange_fn(ctx.cfg.transport)
         with torch.no_grad():
-            dx, d_weights, dw_up, dw_down = layer_torch.backward_loop(
+            dx, d_weights, dw_up, dw_down = layer_torch.backward_pass(
                 x, weights, w_up, w_down, ctx.plan, g_out.contiguous(), ctx.cfg, ctx.group, exchange)
         return dx, None, d_weights, dw_up, dw_down, None, None
 

@@ -6,6 +6,7 @@
 #include "gemm/grouped_gemm.cuh"
 #include "plan/plan_kernel.cuh"
 #include "runtime/fused_rank.h"
+#include "runtime/kernel_runner.h"
 
 namespace {
 
@@ -89,14 +90,29 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("pair_grid_used", []() { return cem::g_pair_grid_used; }, "grid of the last CTA-pair GEMM launch");
   m.def("wait_probe", &wait_probe, "bounded-wait self test kernel");
   m.def("format_status", &cem::format_status, "text of a recorded status block");
+  py::class_<cem::KernelRunner>(m, "KernelRunner")
+      .def(py::init<int, int, int, int, bool>(), py::arg("L"), py::arg("S"), py::arg("stripe"), py::arg("num_sms"),
+           py::arg("cta_pairs") = false)
+      .def("set_groups", &cem::KernelRunner::set_groups)
+      .def("gmm_swiglu", &cem::KernelRunner::gmm_swiglu, py::arg("x"), py::arg("w_up"), py::arg("act"),
+           py::arg("h") = py::none())
+      .def("gmm", &cem::KernelRunner::gmm)
+      .def("gmm_down_dw", &cem::KernelRunner::gmm_down_dw)
+      .def("gmm_dswiglu", &cem::KernelRunner::gmm_dswiglu)
+      .def("tgmm", &cem::KernelRunner::tgmm)
+      .def("check_status", &cem::KernelRunner::check_status);
   py::class_<cem::FusedRank>(m, "FusedRank")
       .def(py::init<int, int, int, int, int, int, int, int, int, int, int, bool, int64_t, std::vector<int64_t>, bool,
-                    int64_t, int, bool>(),
+                    int64_t, int, bool, bool>(),
            py::arg("P"), py::arg("L"), py::arg("me"), py::arg("S"), py::arg("D"), py::arg("F"), py::arg("K"),
            py::arg("stripe"), py::arg("tk_cap"), py::arg("max_slices"), py::arg("num_sms"), py::arg("fp8"),
            py::arg("arena"), py::arg("peer_arenas"), py::arg("use_comm_stream"), py::arg("spin_limit"),
-           py::arg("put_blocks"), py::arg("cta_pairs") = true)
+           py::arg("put_blocks"), py::arg("cta_pairs") = true, py::arg("tgmm_pairs") = true)
       .def("begin_forward", &cem::FusedRank::begin_forward)
+      .def("begin_forward_async", &cem::FusedRank::begin_forward_async)
+      .def("resolve_slices", &cem::FusedRank::resolve_slices)
+      .def("set_pass_slices", &cem::FusedRank::set_pass_slices)
+      .def("set_mbar_limit_us", &cem::FusedRank::set_mbar_limit_us)
       .def("sort_only", &cem::FusedRank::sort_only)
       .def("begin_backward", &cem::FusedRank::begin_backward, py::arg("plan"), py::arg("known_slices") = -1,
            py::arg("known_rows") = -1)

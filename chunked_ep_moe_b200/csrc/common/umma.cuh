@@ -161,6 +161,19 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 // Waits until this thread's committed bulk stores have READ their shared-memory source (it may be overwritten).
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 
+// The same, but the most recently committed group may still be reading (double-buffered staging).
+__device__ __forceinline__ void bulk_wait_read_but_one() {
+  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+}
+
+// Tiled 2-D store, this CTA's shared memory -> global memory through a tensor map (box and swizzle from the map);
+// x is the first column (a multiple of 8 bf16 elements), y the first row. Tracked like a bulk store.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_src), "r"(x), "r"(y)
+               : "memory");
+}
+
 // Waits until this thread's committed bulk stores have completed (their writes are done).
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 

@@ -100,8 +100,8 @@ __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)
 // rank s so far; `flush_returned` releases them once, after the CTA's last tile.
 template <int MODE>
 __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl, uint32_t tacc, int q, int lane,
-                                             uint8_t* stage_gen, uint32_t& returned, int col0 = 0,
-                                             int ncols = kBlockN) {
+                                             uint8_t* stage_gen, uint32_t& returned, const CUtensorMap* map_c,
+                                             int col0 = 0, int ncols = kBlockN) {
   using Traits = ModeTraits<MODE>;
   const int row = q * 32 + lane;  // tile row owned by this thread
   const int grow = tl.row0 + row;
@@ -315,43 +315,50 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
       }
     };
     if (final) {
-      // bf16 gradient: every lane stages 128 columns (256 bytes) of its own row and stores them with one bulk copy,
-      // so the gradient leaves in full lines through the async proxy and the warp never waits for a store.
-      __nv_bfloat16* my_out = p.grad_out + static_cast<size_t>(tl.g) * m_total * n_total + row_off;
-      uint8_t* my_row = stage_gen + lane * kStageRowPitch;
-      const uint32_t my_row_s = smem_u32(my_row);
-      auto stage_chunk = [&](int c, const uint32_t (&v)[32]) {  // c: 32-column chunk inside the 128-column piece
+      // bf16 gradient: the warp stages 32 rows x 64 columns at a time in the tensor map's swizzled layout (8 KB of
+      // staging = two such blocks, so one block is filled while the other is being stored) and one lane hands each
+      // block to the TMA as a tiled store: 16 stores of 4 KB per 128 x 256 tile, full lines, nobody waits for them.
+      // (One 256-byte bulk store per lane and half tile was measured here and is slower: 256 small copies per tile
+      // against ~4 k-blocks of MMA work.)
+      const int out_row0 = tl.g * static_cast<int>(m_total) + tl.m * kBlockM + q * 32;  // in the [L*M, N] view
+#pragma unroll 1
+      for (int ch = 0; ch < ncols / 64; ++ch) {
+        const int col = col0 + ch * 64;
+        uint8_t* blk = stage_gen + (ch & 1) * 4096;
+        if (lane == 0) bulk_wait_read_but_one();  // the store that last read this block is done with it
+        __syncwarp();
+        uint32_t r2[32];
+        if (first && tl.kblocks > 0) {
+          // Common case (the expert lies inside one slice): two TMEM loads per wait.
+          tmem_ld_32x32(tacc + col, r);
+          tmem_ld_32x32(tacc + col + 32, r2);
+          tmem_ld_wait();
+        } else {
+          load_chunk(col + 32);
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-          *reinterpret_cast<int4*>(my_row + (c * 4 + i) * 16) =
-              make_int4(pack_bf16(__uint_as_float(v[8 * i]), __uint_as_float(v[8 * i + 1])),
-                        pack_bf16(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3])),
-                        pack_bf16(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5])),
-                        pack_bf16(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7])));
-      };
-#pragma unroll 1
-      for (int col = col0; col < col0 + ncols; col += 128) {
-        bulk_wait_read();  // my previous store has read this staging row
-#pragma unroll 1
-        for (int c = 0; c < 4; c += 2) {
-          if (first && tl.kblocks > 0) {
-            // Common case (the expert lies inside one slice): two TMEM loads per wait.
-            uint32_t r2[32];
-            tmem_ld_32x32(tacc + col + c * 32, r);
-            tmem_ld_32x32(tacc + col + c * 32 + 32, r2);
-            tmem_ld_wait();
-            stage_chunk(c, r);
-            stage_chunk(c + 1, r2);
-          } else {
-            load_chunk(col + c * 32);
-            stage_chunk(c, r);
-            load_chunk(col + c * 32 + 32);
-            stage_chunk(c + 1, r);
-          }
+          for (int i = 0; i < 32; ++i) r2[i] = r[i];
+          load_chunk(col);
+        }
+        uint8_t* my_row = blk + lane * 128;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          *reinterpret_cast<int4*>(my_row + ((i ^ (lane & 7)) << 4)) =
+              make_int4(pack_bf16(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])),
+                        pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
+                        pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])),
+                        pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7])));
+          *reinterpret_cast<int4*>(my_row + (((4 + i) ^ (lane & 7)) << 4)) =
+              make_int4(pack_bf16(__uint_as_float(r2[8 * i]), __uint_as_float(r2[8 * i + 1])),
+                        pack_bf16(__uint_as_float(r2[8 * i + 2]), __uint_as_float(r2[8 * i + 3])),
+                        pack_bf16(__uint_as_float(r2[8 * i + 4]), __uint_as_float(r2[8 * i + 5])),
+                        pack_bf16(__uint_as_float(r2[8 * i + 6]), __uint_as_float(r2[8 * i + 7])));
         }
         fence_proxy_async_smem();
-        bulk_store(reinterpret_cast<unsigned long long>(my_out + col), my_row_s, 256);
-        bulk_commit();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(map_c, smem_u32(blk), tl.n * kBlockN + col, out_row0);
+          bulk_commit();
+        }
       }
     } else {
 #pragma unroll 1

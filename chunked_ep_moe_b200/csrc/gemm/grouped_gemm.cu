@@ -56,7 +56,7 @@ constexpr int epilogue_warps() { return 4; }
 template <int MODE>
 __global__ void __launch_bounds__(64 + 32 * epilogue_warps<MODE>(), 1)
 grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap map_a,
-                    const __grid_constant__ CUtensorMap map_b) {
+                    const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c) {
   using Traits = ModeTraits<MODE>;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled tiles want 1024-byte aligned bases.
@@ -110,6 +110,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
     mbar_init_fence();
     tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_b);
+    if constexpr (MODE == kModeTgmm) tma_prefetch_desc(&map_c);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
@@ -134,8 +135,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
       // the copies), so stage index, phase and addresses stay warp-uniform values.
       uint32_t ps = 0, pph = 0;
       bool dead = false;
+      // The next tile is decoded one iteration ahead, so its plan-table load is in flight while this tile runs.
+      Tile nxt = {};
+      if (blockIdx.x < num_tiles) nxt = decode_tile<MODE>(p, blockIdx.x, num_entries);
       for (int t = blockIdx.x; t < num_tiles && !dead && !*abort_flag; t += gridDim.x) {
-        const Tile tl = decode_tile<MODE>(p, t, num_entries);
+        const Tile tl = nxt;
+        if (t + static_cast<int>(gridDim.x) < num_tiles) nxt = decode_tile<MODE>(p, t + static_cast<int>(gridDim.x), num_entries);
         if constexpr (MODE == kModeSwiglu) {
           if (p.arrive != nullptr && tl.g != waited_expert) {
             if (!wait_expert_rows(p, tl.g, lane, abort_flag)) break;
@@ -218,8 +223,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
         }
         dead = true;
       };
+      // The next tile is decoded one iteration ahead, so its plan-table load is in flight while this tile runs.
+      Tile nxt = {};
+      if (blockIdx.x < num_tiles) nxt = decode_tile<MODE>(p, blockIdx.x, num_entries);
       for (int t = blockIdx.x; t < num_tiles && !dead && !*abort_flag; t += gridDim.x, ++tcount) {
-        const Tile tl = decode_tile<MODE>(p, t, num_entries);
+        const Tile tl = nxt;
+        if (t + static_cast<int>(gridDim.x) < num_tiles) nxt = decode_tile<MODE>(p, t + static_cast<int>(gridDim.x), num_entries);
         const int as = tcount & 1;
         const uint32_t aph = (tcount >> 1) & 1u;
         const uint32_t tmem_d = tmem_base + as * kBlockN;
@@ -302,11 +311,17 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
     constexpr int kColsPerWarp = kBlockN * 4 / epilogue_warps<MODE>();  // warps sharing a lane quarter split the columns
     const int col0 = (ew >> 2) * kColsPerWarp;
     const int ncols = kColsPerWarp;
-    uint8_t* stage_gen = staging_gen + ew * (kStagingBytes / epilogue_warps<MODE>());
+    // Weight gradients stage swizzled 4 KB blocks for tiled TMA stores (1024-byte aligned, 8 KB per warp); every other
+    // mode stages padded rows.
+    uint8_t* stage_gen = staging_gen + ew * (MODE == kModeTgmm ? 8192 : kStagingBytes / epilogue_warps<MODE>());
     uint32_t tcount = 0, returned = 0;
     long long epi_wait = 0;
+    // The next tile is decoded one iteration ahead, so its plan-table load is in flight while this tile runs.
+    Tile nxt = {};
+    if (blockIdx.x < num_tiles) nxt = decode_tile<MODE>(p, blockIdx.x, num_entries);
     for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x, ++tcount) {
-      const Tile tl = decode_tile<MODE>(p, t, num_entries);
+      const Tile tl = nxt;
+      if (t + static_cast<int>(gridDim.x) < num_tiles) nxt = decode_tile<MODE>(p, t + static_cast<int>(gridDim.x), num_entries);
       const int as = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1u;
       const long long w0 = counting ? clock64() : 0;
@@ -320,7 +335,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
       if (!ok) break;
       tcgen05_fence_after_sync();
       const uint32_t tacc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * kBlockN;
-      run_epilogue<MODE>(p, tl, tacc, q, lane, stage_gen, returned, col0, ncols);
+      run_epilogue<MODE>(p, tl, tacc, q, lane, stage_gen, returned, &map_c, col0, ncols);
       // Hand the accumulator buffer back to the MMA warp.
       tcgen05_fence_before_sync();
       __syncwarp();
@@ -342,8 +357,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
 
 }  // namespace
 
-void launch_grouped_gemm(int mode, const GemmParams& p, const CUtensorMap& map_a, const CUtensorMap& map_b, int grid,
-                         cudaStream_t stream) {
+void launch_grouped_gemm(int mode, const GemmParams& p, const CUtensorMap& map_a, const CUtensorMap& map_b,
+                         const CUtensorMap& map_c, int grid, cudaStream_t stream) {
 #define CEM_LAUNCH(M)                                                                                         \
   case M: {                                                                                                   \
     static bool configured = false;                                                                           \
@@ -351,7 +366,7 @@ void launch_grouped_gemm(int mode, const GemmParams& p, const CUtensorMap& map_a
       cudaFuncSetAttribute(grouped_gemm_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes); \
       configured = true;                                                                                      \
     }                                                                                                         \
-    grouped_gemm_kernel<M><<<grid, 64 + 32 * epilogue_warps<M>(), kGemmSmemBytes, stream>>>(p, map_a, map_b);   \
+    grouped_gemm_kernel<M><<<grid, 64 + 32 * epilogue_warps<M>(), kGemmSmemBytes, stream>>>(p, map_a, map_b, map_c);   \
     break;                                                                                                    \
   }
   switch (mode) {

@@ -92,14 +92,16 @@ constexpr int kSmemTailBytes = 256;   // barriers, TMEM slot, flags
 constexpr int kGemmSmemBytes = kSmemAlignSlack + kStages * kStageBytes + kStagingBytes + kSmemTailBytes;
 static_assert(kGemmSmemBytes <= 232448, "more shared memory than one CTA can have");
 
-void launch_grouped_gemm(int mode, const GemmParams& p, const CUtensorMap& map_a, const CUtensorMap& map_b, int grid,
-                         cudaStream_t stream);
+// `map_c`: weight-gradient mode only, the bf16 gradient [L*M, N] with boxes of 32 rows x 64 columns (tiled stores);
+// the other modes ignore it (pass any valid map).
+void launch_grouped_gemm(int mode, const GemmParams& p, const CUtensorMap& map_a, const CUtensorMap& map_b,
+                         const CUtensorMap& map_c, int grid, cudaStream_t stream);
 
 // CTA-pair variant (clusters of two CTAs, one 256 x 256 MMA per pair). Same parameters; K-major weight
 // maps must use 128-row boxes (each CTA loads its own half of the column tile). `grid` is rounded down
 // to an even number.
 extern int g_pair_grid_used;  // grid of the last CTA-pair launch (clamped to what is resident at once)
 void launch_grouped_gemm_pair(int mode, const GemmParams& p, const CUtensorMap& map_a, const CUtensorMap& map_b,
-                              int grid, cudaStream_t stream);
+                              const CUtensorMap& map_c, int grid, cudaStream_t stream);
 
 }  // namespace cem

@@ -83,7 +83,7 @@ __device__ __forceinline__ void issue_pair_kblock(const GemmParams& p, const Til
 template <int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap map_a,
-                         const __grid_constant__ CUtensorMap map_b) {
+                         const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c) {
   using Traits = ModeTraits<MODE>;
   // Weight-gradient k-blocks may need rows zeroed by the CTA that owns them, so that mode keeps a CTA-local full
   // barrier and relays "my half is ready" to the leader; every other mode lets the TMA credit the leader directly.
@@ -148,6 +148,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
     mbar_init_fence();
     tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_b);
+    if constexpr (MODE == kModeTgmm) tma_prefetch_desc(&map_c);
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, 512);
@@ -173,8 +174,12 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
       // The whole warp walks the k-blocks in step; one elected lane issues the copies.
       uint32_t ps = 0, pph = 0;
       bool dead = false;
+      // The next tile is decoded one iteration ahead, so its plan-table load is in flight while this tile runs.
+      Tile nxt = {};
+      if (first_tile < num_tiles) nxt = decode_pair_tile<MODE>(p, first_tile, num_entries, rank);
       for (int t = first_tile; t < num_tiles && !dead && !*abort_flag; t += tile_step) {
-        const Tile tl = decode_pair_tile<MODE>(p, t, num_entries, rank);
+        const Tile tl = nxt;
+        if (t + tile_step < num_tiles) nxt = decode_pair_tile<MODE>(p, t + tile_step, num_entries, rank);
         if constexpr (MODE == kModeSwiglu) {
           if (p.arrive != nullptr && tl.g != waited_expert) {
             if (!wait_expert_rows(p, tl.g, lane, abort_flag)) break;
@@ -255,8 +260,12 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
         ++it;
         if (++cs == kPairStages) { cs = 0; cph ^= 1u; }
       };
+      // The next tile is decoded one iteration ahead, so its plan-table load is in flight while this tile runs.
+      Tile nxt = {};
+      if (first_tile < num_tiles) nxt = decode_pair_tile<MODE>(p, first_tile, num_entries, rank);
       for (int t = first_tile; t < num_tiles && !dead && !*abort_flag && (kRelay || leader); t += tile_step, ++tcount) {
-        const Tile tl = decode_pair_tile<MODE>(p, t, num_entries, rank);
+        const Tile tl = nxt;
+        if (t + tile_step < num_tiles) nxt = decode_pair_tile<MODE>(p, t + tile_step, num_entries, rank);
         const int as = tcount & 1;
         const uint32_t aph = (tcount >> 1) & 1u;
         const uint32_t tmem_d = tmem_base + as * kBlockN;
@@ -339,11 +348,15 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
   } else {
     // ================================ epilogue (both CTAs) ==================================
     const int q = warp & 3;
-    uint8_t* stage_gen = staging_gen + (warp - 2) * (kStagingBytes / 4);
+    uint8_t* stage_gen = staging_gen + (warp - 2) * (MODE == kModeTgmm ? 8192 : kStagingBytes / 4);
     const uint32_t leader_acc_empty0 = map_to_cta(acc_empty_bar(0), 0);
     uint32_t tcount = 0, returned = 0;
+    // The next tile is decoded one iteration ahead, so its plan-table load is in flight while this tile runs.
+    Tile nxt = {};
+    if (first_tile < num_tiles) nxt = decode_pair_tile<MODE>(p, first_tile, num_entries, rank);
     for (int t = first_tile; t < num_tiles && !*abort_flag; t += tile_step, ++tcount) {
-      const Tile tl = decode_pair_tile<MODE>(p, t, num_entries, rank);
+      const Tile tl = nxt;
+      if (t + tile_step < num_tiles) nxt = decode_pair_tile<MODE>(p, t + tile_step, num_entries, rank);
       const int as = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1u;
       bool ok = mbar_wait_poll(acc_full_bar(as), aph, p.mbar_limit);
@@ -355,7 +368,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
       if (!ok) break;
       tcgen05_fence_after_sync();
       const uint32_t tacc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * kBlockN;
-      run_epilogue<MODE>(p, tl, tacc, q, lane, stage_gen, returned);
+      run_epilogue<MODE>(p, tl, tacc, q, lane, stage_gen, returned, &map_c);
       tcgen05_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(leader_acc_empty0 + 8u * as);
@@ -404,7 +417,7 @@ int resident_pair_grid(Kernel kernel, int requested) {
 int g_pair_grid_used = 0;  // last pair grid size, for diagnostics
 
 void launch_grouped_gemm_pair(int mode, const GemmParams& p, const CUtensorMap& map_a, const CUtensorMap& map_b,
-                              int grid, cudaStream_t stream) {
+                              const CUtensorMap& map_c, int grid, cudaStream_t stream) {
   grid &= ~1;  // whole pairs only
 #define CEM_LAUNCH_PAIR(M)                                                                                       \
   case M: {                                                                                                      \
@@ -416,7 +429,7 @@ void launch_grouped_gemm_pair(int mode, const GemmParams& p, const CUtensorMap& 
     }                                                                                                            \
     const int g = grid < resident ? grid : resident;                                                             \
     g_pair_grid_used = g;                                                                                        \
-    grouped_gemm_pair_kernel<M><<<g, kGemmThreads, kGemmSmemBytes, stream>>>(p, map_a, map_b);                   \
+    grouped_gemm_pair_kernel<M><<<g, kGemmThreads, kGemmSmemBytes, stream>>>(p, map_a, map_b, map_c);                   \
     break;                                                                                                       \
   }
   switch (mode) {

@@ -51,6 +51,7 @@ extern "C" int cem_expert_sort_noalloc(const int* expert_ids, int n, int num_exp
   // Every (expert, block) entry the scan and scatter kernels read is first written by the histogram
   // kernel of this same call, so stale contents from an earlier call are never observed.
   cem::launch_expert_sort(expert_ids, n, num_experts, order, inv_order, counts, scratch, stream);
-  err = cudaGetLastError();
+  // Peek, not get: an error some earlier call of the caller left behind stays where it is.
+  err = cudaPeekAtLastError();
   return err == cudaSuccess ? 0 : static_cast<int>(err);
 }

@@ -19,8 +19,15 @@
 //
 // Limits: 1 <= n <= 524288 ids, 1 <= num_experts <= 1024. Larger problems are rejected.
 //
+// Precondition: every id lies in [0, num_experts). The kernels never read or write out of bounds for other
+// values, but such ids are left out of the sort: `counts` does not count them, their `inv_order` entries and
+// the last entries of `order` keep whatever the buffers held before, and the call still returns 0. Validate
+// ids before the call if they can be wrong.
+//
 // Return value: 0 on success; -1 null pointer; -2 n out of range; -3 num_experts out of range;
-// any positive value is the cudaError_t of a failed runtime call (set-up or launch).
+// any positive value is the cudaError_t of a failed runtime call (set-up or launch). The call does not clear
+// the runtime's sticky error state: it reports an error that is pending when it returns, its own or an older
+// one of the caller's, and leaves it pending.
 //
 // First call on a device: it looks up the device address of the scratch array (one runtime query,
 // no allocation) and remembers it for that device. Make that first call outside of any stream

@@ -46,7 +46,8 @@ __global__ void __launch_bounds__(256) plan_build_kernel(const PlanKernelParams 
 constexpr int kSortThreads = 256;
 constexpr int kSortItems = 8;  // ids per thread; one block covers 2048 consecutive ids
 
-__global__ void __launch_bounds__(kSortThreads) sort_hist_kernel(const int* ids, int n, int num_experts, int* block_hist) {
+__global__ void __launch_bounds__(kSortThreads) sort_hist_kernel(const int* ids, int n, int num_experts, int* block_hist,
+                                                                  StatusBlock* status) {
   extern __shared__ int s_hist[];
   for (int e = threadIdx.x; e < num_experts; e += blockDim.x) s_hist[e] = 0;
   __syncthreads();
@@ -55,7 +56,14 @@ __global__ void __launch_bounds__(kSortThreads) sort_hist_kernel(const int* ids,
     const int idx = base + i;
     if (idx < n) {
       const int e = ids[idx];
-      if (e >= 0 && e < num_experts) atomicAdd(&s_hist[e], 1);
+      if (e >= 0 && e < num_experts) {
+        atomicAdd(&s_hist[e], 1);
+      } else {
+        // An id outside [0, num_experts) has no expert: it is left out of the sort and recorded, so that the pass is
+        // reported as invalid (every later kernel of the pass then returns at once).
+        report_status(status, kStatusBadIndex, kKernelPlan, 1, 0, idx, static_cast<uint32_t>(num_experts),
+                      static_cast<uint32_t>(e));
+      }
     }
   }
   __syncthreads();
@@ -129,10 +137,11 @@ size_t expert_sort_scratch_ints(int n, int num_experts) {
 }
 
 void launch_expert_sort(const int* expert_ids, int n, int num_experts, int* order, int* inv_order, int* counts,
-                        int* scratch, cudaStream_t stream) {
+                        int* scratch, cudaStream_t stream, StatusBlock* status) {
   int blocks = (n + kSortThreads * kSortItems - 1) / (kSortThreads * kSortItems);
   if (blocks < 1) blocks = 1;
-  sort_hist_kernel<<<blocks, kSortThreads, num_experts * sizeof(int), stream>>>(expert_ids, n, num_experts, scratch);
+  sort_hist_kernel<<<blocks, kSortThreads, num_experts * sizeof(int), stream>>>(expert_ids, n, num_experts, scratch,
+                                                                                status);
   sort_scan_kernel<<<1, 256, 0, stream>>>(scratch, num_experts, blocks, counts);
   sort_scatter_kernel<<<blocks, kSortThreads, (num_experts + kSortThreads * kSortItems) * sizeof(int), stream>>>(
       expert_ids, n, num_experts, scratch, order, inv_order);

@@ -33,9 +33,11 @@ void launch_plan_build(const PlanKernelParams& p, cudaStream_t stream);
 void plan_build_host(const int* counts, int* plan, const PlanLayout& lay, int me);
 
 // Stable counting sort of the T*K expert ids: order (send order -> flat index), inverse, histogram.
-// Replaces argsort + scatter-add bincount (src/chunked_moe/plan.py:74-76).
+// Replaces argsort + scatter-add bincount (src/chunked_moe/plan.py:74-76). Ids outside [0, num_experts) take no part
+// in the sort (their `inv_order` entry and the tail of `order` are left untouched); with a status block the first one
+// is recorded as kStatusBadIndex (detail = its position, expected = num_experts, seen = the id).
 void launch_expert_sort(const int* expert_ids, int n, int num_experts, int* order, int* inv_order, int* counts,
-                        int* scratch, cudaStream_t stream);
+                        int* scratch, cudaStream_t stream, StatusBlock* status = nullptr);
 size_t expert_sort_scratch_ints(int n, int num_experts);
 
 }  // namespace cem

@@ -3,6 +3,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -75,10 +76,10 @@ ArenaLayout make_arena_layout(int P, int L, int S, int D, int tk_cap, bool fp8) 
 
 FusedRank::FusedRank(int P, int L, int me, int S, int D, int F, int K, int stripe, int tk_cap, int max_slices,
                      int num_sms, bool fp8, int64_t arena, std::vector<int64_t> peer_arenas, bool use_comm_stream,
-                     int64_t spin_limit, int put_blocks, bool cta_pairs)
+                     int64_t spin_limit, int put_blocks, bool cta_pairs, bool tgmm_pairs)
     : P_(P), L_(L), me_(me), S_(S), D_(D), F_(F), K_(K), stripe_(stripe), tk_cap_(tk_cap), max_slices_(max_slices),
       num_sms_(num_sms), put_blocks_(put_blocks), fp8_(fp8), use_comm_stream_(use_comm_stream),
-      cta_pairs_(cta_pairs && num_sms >= 2) {
+      cta_pairs_(cta_pairs && num_sms >= 2), tgmm_pairs_(tgmm_pairs && num_sms >= 2) {
   expect(P >= 1 && L >= 1 && me >= 0 && me < P, "bad rank geometry");
   expect(static_cast<int>(peer_arenas.size()) == P, "need one arena pointer per rank");
   expect(P <= 32, "at most 32 expert-parallel ranks (one warp lane watches one source)");
@@ -139,7 +140,7 @@ FusedRank::FusedRank(int P, int L, int me, int S, int D, int F, int K, int strip
 
   // TMA descriptors of the local buffers. K-major A tiles are 128 rows, MN-major tiles 64 rows (k) of several
   // 64-column chunks brought by one 3-D copy (a CTA of a pair loads half of the 256-wide column tile).
-  const uint32_t mn_chunks_b = cta_pairs_ ? 2 : 4;
+  const uint32_t mn_chunks_b = tgmm_pairs_ ? 2 : 4;  // the MN-major maps of local buffers feed the weight-gradient mode
   for (int b = 0; b < 2; ++b) {
     const void* xb = arena_ + arena_lay_.xbuf + static_cast<size_t>(b) * S * D * 2;
     map_x_k_[b] = make_bf16_map_2d(xb, S, D, 128);
@@ -163,6 +164,7 @@ FusedRank::FusedRank(int P, int L, int me, int S, int D, int F, int K, int strip
     for (cudaEvent_t* e : {&ev_down_[q], &ev_dd_[q], &ev_ds_[q], &ev_dx_[q], &ev_tgd_[q], &ev_tgu_[q]})
       cuda_check(cudaEventCreateWithFlags(e, cudaEventDisableTiming), "event");
   cuda_check(cudaEventCreateWithFlags(&ev_pass_, cudaEventDisableTiming), "event");
+  cuda_check(cudaEventCreateWithFlags(&ev_header_, cudaEventDisableTiming | cudaEventBlockingSync), "event");
   for (int i = 0; i < 4; ++i) {
     cuda_check(cudaEventCreateWithFlags(&ev_put_[i], cudaEventDisableTiming), "event");
     cuda_check(cudaEventCreateWithFlags(&ev_done_[i], cudaEventDisableTiming), "event");
@@ -180,6 +182,7 @@ FusedRank::~FusedRank() {
       if (e) cudaEventDestroy(e);
   }
   if (ev_pass_) cudaEventDestroy(ev_pass_);
+  if (ev_header_) cudaEventDestroy(ev_header_);
   for (int i = 0; i < 4; ++i) {
     if (ev_put_[i]) cudaEventDestroy(ev_put_[i]);
     if (ev_done_[i]) cudaEventDestroy(ev_done_[i]);
@@ -224,12 +227,12 @@ void FusedRank::sort_only(torch::Tensor expert_ids, torch::Tensor order, torch::
   expect_i32(my_counts, P_ * L_, "my_counts");
   launch_expert_sort(expert_ids.data_ptr<int>(), static_cast<int>(tk), P_ * L_, order.data_ptr<int>(),
                      inv_order.data_ptr<int>(), my_counts.data_ptr<int>(), sort_scratch_.data_ptr<int>(),
-                     current_stream());
+                     current_stream(), reinterpret_cast<StatusBlock*>(status_.data_ptr()));
   launches_ += 3;
 }
 
-int64_t FusedRank::begin_forward(torch::Tensor expert_ids, torch::Tensor plan, torch::Tensor order,
-                                 torch::Tensor inv_order, torch::Tensor counts, bool counts_prefilled) {
+int64_t FusedRank::begin_forward_async(torch::Tensor expert_ids, torch::Tensor plan, torch::Tensor order,
+                                       torch::Tensor inv_order, torch::Tensor counts, bool counts_prefilled) {
   cudaStream_t st = current_stream();
   const int64_t tk = expert_ids.numel();
   expect(tk <= tk_cap_, "T*K exceeds the workspace capacity");
@@ -261,8 +264,51 @@ int64_t FusedRank::begin_forward(torch::Tensor expert_ids, torch::Tensor plan, t
   }
   launch_plan_build(pp, st);
   ++launches_;
-  return begin_backward(plan, -1, -1);
+  // Header and status follow the plan kernel to the host; nobody waits here.
+  cuda_check(cudaMemcpyAsync(host_header_, plan.data_ptr(), 16 * sizeof(int32_t), cudaMemcpyDeviceToHost, st),
+             "plan header copy");
+  cuda_check(cudaMemcpyAsync(host_header_ + 16, status_.data_ptr(), 8 * sizeof(int32_t), cudaMemcpyDeviceToHost, st),
+             "status copy");
+  cuda_check(cudaEventRecord(ev_header_, st), "event record");
+  begin_backward(plan, max_slices_, tk);  // any slice below the workspace's capacity may be launched until resolved
+  return last_slices_ < 0 ? -1 : std::min<int64_t>(last_slices_, max_slices_);
 }
+
+int64_t FusedRank::resolve_slices() {
+  cuda_check(cudaEventSynchronize(ev_header_), "plan header wait");
+  const int32_t* st = host_header_ + 16;
+  if (st[0] != 0) {
+    const std::string message = format_status(std::vector<int64_t>(st, st + 8), me_);
+    cudaStream_t cur = current_stream();
+    cuda_check(cudaStreamSynchronize(cur), "status sync");  // what was launched on the guess ends (at once) first
+    cuda_check(cudaMemsetAsync(status_.data_ptr(), 0, 8 * sizeof(int32_t), cur), "status clear");
+    cuda_check(cudaStreamSynchronize(cur), "status clear sync");
+    throw std::runtime_error(message);
+  }
+  expect(host_header_[4] == 0, "routing needs more slices than the workspace was sized for (max_slices)");
+  expect(host_header_[5] == cur_rows_, "the routing plan does not account for every token copy");
+  last_slices_ = host_header_[0];
+  return last_slices_;
+}
+
+void FusedRank::set_pass_slices(int64_t launched) {
+  expect(launched >= 0 && launched <= max_slices_, "slice count exceeds the workspace");
+  cur_slices_ = launched;
+}
+
+void FusedRank::set_mbar_limit_us(int64_t us) {
+  expect(us > 0 && us <= 600ll * 1000 * 1000, "barrier limit must be between 1 us and 600 s");
+  mbar_limit_ = static_cast<uint32_t>(us);
+}
+
+int64_t FusedRank::begin_forward(torch::Tensor expert_ids, torch::Tensor plan, torch::Tensor order,
+                                 torch::Tensor inv_order, torch::Tensor counts, bool counts_prefilled) {
+  begin_forward_async(expert_ids, plan, order, inv_order, counts, counts_prefilled);
+  const int64_t n = resolve_slices();
+  set_pass_slices(n);
+  return n;
+}
+
 
 int64_t FusedRank::begin_backward(torch::Tensor plan, int64_t known_slices, int64_t known_rows) {
   cudaStream_t st = current_stream();
@@ -400,13 +446,14 @@ void FusedRank::set_pipeline_counters(c10::optional<torch::Tensor> counters) {
 }
 
 void FusedRank::launch_gemm(int mode, const GemmParams& p0, const CUtensorMap& a, const CUtensorMap& b,
-                            cudaStream_t st) {
+                            cudaStream_t st, const CUtensorMap* c) {
   GemmParams p = p0;
   if (prof_.defined())
     p.prof = reinterpret_cast<unsigned long long*>(prof_.data_ptr<int64_t>()) +
              static_cast<size_t>(mode) * prof_.size(1) * kProfSlots;
-  if (cta_pairs_) launch_grouped_gemm_pair(mode, p, a, b, num_sms_, st);
-  else launch_grouped_gemm(mode, p, a, b, num_sms_, st);
+  const CUtensorMap& out = c != nullptr ? *c : a;
+  if (mode == kModeTgmm ? tgmm_pairs_ : cta_pairs_) launch_grouped_gemm_pair(mode, p, a, b, out, num_sms_, st);
+  else launch_grouped_gemm(mode, p, a, b, out, num_sms_, st);
   ++launches_;
 }
 
@@ -545,7 +592,7 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
     p.carry_in = carry_down_.data_ptr<float>() + static_cast<size_t>(par ^ 1) * F_ * D_;
     p.carry_out = carry_down_.data_ptr<float>() + static_cast<size_t>(par) * F_ * D_;
     p.grad_out = reinterpret_cast<__nv_bfloat16*>(dw_down.data_ptr());
-    launch_gemm(kModeTgmm, p, map_act_mn_[q], map_dy_mn_[q], aux);
+    launch_gemm(kModeTgmm, p, map_act_mn_[q], map_dy_mn_[q], aux, &weight_map(dw_down, 32));
   }
   if (async) {
     cuda_check(cudaEventRecord(ev_tgd_[q], aux), "event record");
@@ -572,7 +619,7 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
     p.carry_in = carry_up_.data_ptr<float>() + static_cast<size_t>(par ^ 1) * D_ * 2 * F_;
     p.carry_out = carry_up_.data_ptr<float>() + static_cast<size_t>(par) * D_ * 2 * F_;
     p.grad_out = reinterpret_cast<__nv_bfloat16*>(dw_up.data_ptr());
-    launch_gemm(kModeTgmm, p, map_x_mn_[b], map_dh_mn_[q], aux);
+    launch_gemm(kModeTgmm, p, map_x_mn_[b], map_dh_mn_[q], aux, &weight_map(dw_up, 32));
   }
   if (async) cuda_check(cudaEventRecord(ev_tgu_[q], aux), "event record");
   launch_slice_done(table<uint32_t>(kTabCredit), P_, me_, seq, aux);

@@ -41,7 +41,7 @@ class FusedRank {
  public:
   FusedRank(int P, int L, int me, int S, int D, int F, int K, int stripe, int tk_cap, int max_slices, int num_sms,
             bool fp8, int64_t arena, std::vector<int64_t> peer_arenas, bool use_comm_stream, int64_t spin_limit,
-            int put_blocks, bool cta_pairs);
+            int put_blocks, bool cta_pairs, bool tgmm_pairs);
   ~FusedRank();
 
   // Forward pass set-up: sort, traffic exchange, plan tables, arrival targets. `plan`, `order`,
@@ -50,6 +50,18 @@ class FusedRank {
   // Returns the number of slices (this synchronises the host with the plan kernel once).
   int64_t begin_forward(torch::Tensor expert_ids, torch::Tensor plan, torch::Tensor order, torch::Tensor inv_order,
                         torch::Tensor counts, bool counts_prefilled);
+  // The same set-up without waiting for the device: the plan header and the status block are copied to pinned host
+  // memory behind the plan kernel and an event is recorded. Returns the slice count of this workspace's previous
+  // forward pass (-1 if there was none) as a GUESS; the caller may launch that many slices at once, then calls
+  // `resolve_slices()` for the real count, launches what is still missing and reports what it launched with
+  // `set_pass_slices()`. Slices past the real count find empty tables and do nothing, on every rank alike.
+  int64_t begin_forward_async(torch::Tensor expert_ids, torch::Tensor plan, torch::Tensor order,
+                              torch::Tensor inv_order, torch::Tensor counts, bool counts_prefilled);
+  // Waits for the header copy (not for the stream), raises a recorded kernel error, returns the real slice count.
+  int64_t resolve_slices();
+  void set_pass_slices(int64_t launched);
+  // Microseconds a pipeline barrier inside a GEMM may take before the kernel gives up (default 20 s).
+  void set_mbar_limit_us(int64_t us);
   // Lockstep harness only: sort + histogram without the exchange (fills order, inv_order, my row of counts).
   void sort_only(torch::Tensor expert_ids, torch::Tensor order, torch::Tensor inv_order, torch::Tensor my_counts);
   // `known_slices`, `known_rows` (T*K): what the forward of the same plan returned / was given; when both are >= 0
@@ -86,10 +98,14 @@ class FusedRank {
   // `chunks` > 0: the MN-major description (64-column chunks, `chunks` of them per copy); 0: plain 2-D boxes.
   const CUtensorMap& weight_map(const torch::Tensor& w, uint32_t box_rows, uint32_t chunks = 0);
   void dequant(const int* plan, int j, int b, bool with_g, cudaStream_t st);
-  void launch_gemm(int mode, const GemmParams& p, const CUtensorMap& a, const CUtensorMap& b, cudaStream_t st);
+  // `c`: the output's tensor map (weight-gradient mode: tiled stores of the bf16 gradient); null otherwise.
+  void launch_gemm(int mode, const GemmParams& p, const CUtensorMap& a, const CUtensorMap& b, cudaStream_t st,
+                   const CUtensorMap* c = nullptr);
 
   int P_, L_, me_, S_, D_, F_, K_, stripe_, tk_cap_, max_slices_, num_sms_, put_blocks_;
-  bool fp8_, use_comm_stream_, cta_pairs_;
+  // `cta_pairs_`: the row-wise GEMM modes run as CTA pairs (256-row tiles). `tgmm_pairs_`: the weight-gradient mode
+  // does; its pairs split the dense feature dimension, so they cost no token padding and are on by default.
+  bool fp8_, use_comm_stream_, cta_pairs_, tgmm_pairs_;
   uint32_t spin_limit_, mbar_limit_;
   PlanLayout lay_;
   ArenaLayout arena_lay_;
@@ -112,7 +128,8 @@ class FusedRank {
 
   cudaStream_t comm_stream_ = nullptr, aux_stream_ = nullptr, chain_[2] = {};
   cudaEvent_t ev_down_[2] = {}, ev_dd_[2] = {}, ev_ds_[2] = {}, ev_dx_[2] = {}, ev_tgd_[2] = {}, ev_tgu_[2] = {};
-  cudaEvent_t ev_pass_ = nullptr, ev_put_[4] = {}, ev_done_[4] = {};
+  cudaEvent_t ev_pass_ = nullptr, ev_put_[4] = {}, ev_done_[4] = {}, ev_header_ = nullptr;
+  int64_t last_slices_ = -1;  // slice count of the previous forward pass (the next pass's guess)
   int32_t* host_header_ = nullptr;  // pinned: 16 plan header ints + 8 status ints
 
   uint32_t seq_ = 0;          // global slice sequence number of the next pass's first slice

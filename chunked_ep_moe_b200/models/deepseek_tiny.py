@@ -125,6 +125,17 @@ class Router(nn.Module):
         self.register_buffer("routed_bias", torch.zeros(cfg.num_experts))
         self.register_buffer("load_counts", torch.zeros(cfg.num_experts))  # bias-update counts of the step
 
+    def _apply(self, fn, *args, **kwargs):
+        # `.to(dtype=bfloat16)` must not touch the balancing state: per-expert counts in the thousands and bias steps
+        # of 1e-3 both vanish in bf16 rounding. Devices still follow the module.
+        keep = {name: buf for name, buf in (("routed_bias", self.routed_bias), ("load_counts", self.load_counts))}
+        super()._apply(fn, *args, **kwargs)
+        for name, old in keep.items():
+            new = getattr(self, name)
+            if new.dtype != torch.float32:
+                setattr(self, name, old.to(device=new.device, dtype=torch.float32))
+        return self
+
     def forward(self, x):
         cfg = self.cfg
         scores = torch.sigmoid(F.linear(x.float(), self.weight.float()))  # [T, E]

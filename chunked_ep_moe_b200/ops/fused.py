@@ -1,8 +1,10 @@
 """The fused NVLink path: `chunked_moe` on the sm_100a kernels (`transport="nvshmem"`, `expert_compute="fused"`).
 
 Per pass the host launches, per slice, a put kernel on the comm stream and a handful of grouped
-tcgen05 GEMMs on the compute stream; everything between ranks happens inside those kernels
-(peer stores, arrival counters, credits). Compared with the reference's loop
+tcgen05 GEMMs on the compute streams; everything between ranks happens inside those kernels
+(peer stores, arrival counters, credits). The host never waits for the device inside a pass: the
+slice count of a forward is guessed from the previous pass and corrected once its real value has
+reached the host. Compared with the reference's loop
 (src/chunked_moe/moe.py:96-119, :148-206):
 
   * no `[T*K, D]` send buffer: the put kernel gathers rows straight from `x[token]`;
@@ -33,6 +35,7 @@ _DEFAULT_SPIN_LIMIT = 1 << 24  # polls (~0.3 us each) before a wait on another r
 _PUT_BLOCKS = 128  # measured: 128 blocks finish a put soonest and disturb the GEMM beside it least
 
 _workspaces: dict = {}
+_retired: list = []  # workspaces replaced by `reserve()`; passes in flight may still hold them
 
 #: Pass as `group` to run the fused kernels on this rank alone (a 1-rank expert-parallel world), whatever
 #: process groups exist. Used by `ops.fused_expert` to serve `expert_compute="fused"` on collective transports.
@@ -78,29 +81,75 @@ class FusedWorkspace:
             num_sms=int(os.environ.get("CEM_GEMM_GRID", cfg.num_sms)), fp8=self.fp8,
             arena=self.arena.local, peer_arenas=self.arena.peers, use_comm_stream=True,
             spin_limit=int(os.environ.get("CEM_SPIN_LIMIT", _DEFAULT_SPIN_LIMIT)), put_blocks=int(os.environ.get("CEM_PUT_BLOCKS", _PUT_BLOCKS)),
-            cta_pairs=use_cta_pairs(tk_cap, self.local_experts))
+            cta_pairs=use_cta_pairs(tk_cap, self.local_experts),
+            tgmm_pairs=os.environ.get("CEM_TGMM_PAIRS", "1") != "0")
+        if "CEM_MBAR_LIMIT_US" in os.environ:
+            self.rank.set_mbar_limit_us(int(os.environ["CEM_MBAR_LIMIT_US"]))
         self.plan_ints = self.rank.plan_ints()
         self.dummy_counts = torch.zeros(1, dtype=torch.int32, device="cuda")
 
 
+def _workspace_key(cfg: ChunkedMoEConfig, group, hidden: int, ffn: int):
+    # The process group OBJECT is part of the key (not its id): the dictionary keeps it alive, so a later group can
+    # never be mistaken for it.
+    return (group, cfg.num_experts, cfg.top_k, cfg.slice_size, cfg.stripe_width, cfg.comm_dtype, cfg.num_sms, hidden,
+            ffn, torch.cuda.current_device())
+
+
 def get_workspace(cfg: ChunkedMoEConfig, group, hidden: int, ffn: int, tokens_times_k: int) -> FusedWorkspace:
-    key = (group if group is SOLO else (id(group) if group is not None else 0), cfg.num_experts, cfg.top_k, cfg.slice_size, cfg.stripe_width,
-           cfg.comm_dtype, cfg.num_sms, hidden, ffn, torch.cuda.current_device())
+    """The cached workspace for this geometry and group; the first call creates it (collectively).
+
+    A workspace never shrinks, moves or is freed behind a pass that still holds it: its capacity is fixed when it is
+    created (the largest `T*K` over the ranks at that moment). A later call that needs more gets a new, larger one
+    when this rank is alone; among several ranks it raises, because making room is a collective decision:
+    `reserve()` is the way to do that.
+    """
+    key = _workspace_key(cfg, group, hidden, ffn)
     ws = _workspaces.get(key)
-    if ws is None or ws.tk_cap < tokens_times_k:
-        if ws is not None:
-            ws.arena.close()
+    if ws is None:
         ws = FusedWorkspace(cfg, group, hidden, ffn, tokens_times_k)
+        _workspaces[key] = ws
+    elif ws.tk_cap < tokens_times_k and ws.world == 1:
+        ws = reserve(cfg, group, hidden, ffn, tokens_times_k)  # nobody to agree with: make room right away
+    elif ws.tk_cap < tokens_times_k:
+        raise RuntimeError(
+            f"chunked_moe fused path: this call has {tokens_times_k} token copies but the workspace of this geometry "
+            f"was created for {ws.tk_cap}. Capacity is agreed between the ranks when the workspace is created; call "
+            f"ops.fused.reserve(cfg, group, hidden, ffn, tokens_times_k) on every rank first.")
+    return ws
+
+
+def reserve(cfg: ChunkedMoEConfig, group, hidden: int, ffn: int, tokens_times_k: int) -> FusedWorkspace:
+    """Collective: makes sure the workspace of this geometry holds `tokens_times_k` token copies on every rank.
+
+    A workspace that is too small is replaced, not freed: passes whose backward has not run yet keep using the arena
+    they started with, and the old workspace is only released by `release_workspaces()`.
+    """
+    key = _workspace_key(cfg, group, hidden, ffn)
+    ws = _workspaces.get(key)
+    need = tokens_times_k
+    if dist.is_available() and dist.is_initialized() and group is not SOLO and dist.get_world_size(group) > 1:
+        t = torch.tensor([need, ws.tk_cap if ws is not None else 0], device="cuda", dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        need, have = int(t[0]), int(t[1])
+    else:
+        have = ws.tk_cap if ws is not None else 0
+    if ws is None or have < need:  # every rank takes the same branch: both numbers are maxima over the ranks
+        if ws is not None:
+            _retired.append(ws)
+        ws = FusedWorkspace(cfg, group, hidden, ffn, need)
         _workspaces[key] = ws
     return ws
 
 
 def release_workspaces() -> None:
-    """Frees every cached workspace (collective when a process group is involved)."""
-    for ws in list(_workspaces.values()):
+    """Frees every workspace, cached or replaced (collective when a process group is involved). A pass whose backward
+    has not run yet must not be kept across this call: its backward raises."""
+    for ws in list(_workspaces.values()) + _retired:
         ws.rank = None
         ws.arena.close()
     _workspaces.clear()
+    _retired.clear()
 
 
 def last_plan_stats(cfg: ChunkedMoEConfig) -> list:
@@ -214,21 +263,32 @@ class _ChunkedMoEFused(torch.autograd.Function):
         rank = ws.rank
         dev = x.device
         plan = torch.empty(ws.plan_ints, dtype=torch.int32, device=dev)
-        order = torch.empty(tokens * cfg.top_k, dtype=torch.int32, device=dev)
-        inv_order = torch.empty_like(order)
+        order = torch.zeros(tokens * cfg.top_k, dtype=torch.int32, device=dev)  # no stray indices if an id is invalid
+        inv_order = torch.zeros_like(order)
         ids32 = expert_ids.to(torch.int32).contiguous()
         w_flat = weights.detach().float().reshape(-1).contiguous()
         xc, w_up_c, w_down_c = x.detach().contiguous(), w_up.detach().contiguous(), w_down.detach().contiguous()
+        def run_slices(lo: int, hi: int) -> None:
+            if hi <= lo:
+                return
+            rank.put(lo, plan, order, xc, None, w_flat)
+            for j in range(lo, hi):
+                with nvtx(f"chunked_moe/fwd slice {j}"):
+                    if j + 1 < hi:
+                        rank.put(j + 1, plan, order, xc, None, w_flat)  # slice j+1 is in flight while slice j computes
+                    rank.compute_forward(j, plan, w_up_c, w_down_c)
+
+        # The slice count is a device value (it depends on the routing). The host does not wait for it: it launches
+        # as many slices as the previous pass of this workspace needed, THEN reads the real count (by then long on
+        # the host) and launches what is missing. Too many is harmless: a slice past the real count finds empty
+        # tables on every rank. Every rank guesses and learns the same numbers, so all ranks loop alike.
         with nvtx("chunked_moe/plan"):
-            n = rank.begin_forward(ids32, plan, order, inv_order, ws.dummy_counts, False)
+            guess = max(0, rank.begin_forward_async(ids32, plan, order, inv_order, ws.dummy_counts, False))
         out = torch.empty_like(xc)
-        if n > 0:
-            rank.put(0, plan, order, xc, None, w_flat)
-        for j in range(n):
-            with nvtx(f"chunked_moe/fwd slice {j}"):
-                if j + 1 < n:
-                    rank.put(j + 1, plan, order, xc, None, w_flat)  # slice j+1 is in flight while slice j computes
-                rank.compute_forward(j, plan, w_up_c, w_down_c)
+        run_slices(0, guess)
+        n = rank.resolve_slices()  # raises here if an earlier kernel recorded an error (bad expert id, timed-out wait)
+        run_slices(guess, n)
+        rank.set_pass_slices(max(guess, n))
         with nvtx("chunked_moe/combine"):
             rank.finish_forward(inv_order, out)
         ctx.save_for_backward(xc, weights, w_up_c, w_down_c, plan, order, inv_order)
@@ -240,6 +300,8 @@ class _ChunkedMoEFused(torch.autograd.Function):
     def backward(ctx, g_out):
         x, weights, w_up, w_down, plan, order, inv_order = ctx.saved_tensors
         rank = ctx.ws.rank
+        if rank is None or ctx.ws.arena.local == 0:
+            raise RuntimeError("chunked_moe fused path: the workspace of this pass was released before its backward")
         g = g_out.to(x.dtype).contiguous()
         w_flat = weights.detach().float().reshape(-1).contiguous()
         # The slice count is the forward's: nothing is read back, the host never waits for the device here.
@@ -261,6 +323,24 @@ class _ChunkedMoEFused(torch.autograd.Function):
         return dx, None, d_weights.reshape(weights.shape).to(weights.dtype), dw_up, dw_down, None, None
 
 
+def unsupported_reason(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
+                       cfg: ChunkedMoEConfig) -> Optional[str]:
+    """Why these tensors cannot run on the fused kernels (shape or dtype), or None. The caller may then fall back to
+    a collective transport, as the reference's put kernel does for rows it cannot move
+    (src/chunked_moe/transport/nvshmem.py:115-118)."""
+    if x.dtype != torch.bfloat16 or w_up.dtype != torch.bfloat16 or w_down.dtype != torch.bfloat16:
+        return "x, w_up and w_down must be bfloat16"
+    if x.shape[1] % 256 or w_down.shape[1] % 256:
+        return f"D={x.shape[1]} and F={w_down.shape[1]} must be multiples of 256"
+    if cfg.stripe_width not in (32, 64, 128):
+        return f"stripe_width={cfg.stripe_width} must be 32, 64 or 128"
+    if cfg.slice_size % 8:
+        return f"slice_size={cfg.slice_size} must be a multiple of 8"
+    if cfg.accum_dtype != "float32":
+        return f"accum_dtype={cfg.accum_dtype!r}: the kernels accumulate weight gradients in float32"
+    return None
+
+
 def chunked_moe_fused(x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Tensor, w_up: torch.Tensor,
                       w_down: torch.Tensor, cfg: ChunkedMoEConfig,
                       group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
@@ -271,4 +351,5 @@ def chunked_moe_fused(x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.
     _require(x.shape[1] % 256 == 0 and w_down.shape[1] % 256 == 0, "needs D % 256 == 0 and F % 256 == 0")
     _require(cfg.stripe_width in (32, 64, 128), "needs stripe_width in {32, 64, 128}")
     _require(cfg.slice_size % 8 == 0, "needs slice_size % 8 == 0")
+    _require(cfg.accum_dtype == "float32", "weight gradients are accumulated in float32 (accum_dtype)")
     return _ChunkedMoEFused.apply(x, expert_ids, weights, w_up, w_down, cfg, group)

@@ -37,7 +37,7 @@ class LockstepWorld:
             ext.FusedRank(P=world, L=self.local, me=r, S=cfg.slice_size, D=hidden, F=ffn, K=cfg.top_k,
                           stripe=cfg.stripe_width, tk_cap=self.tk, max_slices=self.max_slices, num_sms=cfg.num_sms,
                           fp8=fp8, arena=self.arenas.bases[r], peer_arenas=self.arenas.bases, use_comm_stream=False,
-                          spin_limit=spin_limit, put_blocks=8, cta_pairs=cta_pairs)
+                          spin_limit=spin_limit, put_blocks=8, cta_pairs=cta_pairs, tgmm_pairs=cta_pairs)
             for r in range(world)
         ]
         self.plan_ints = self.ranks[0].plan_ints()

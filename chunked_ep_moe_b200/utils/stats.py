@@ -1,7 +1,7 @@
 """Per-step observability that falls out of the plan for free.
 
 The reference has no counters or logging (only prints in its compile script). These helpers turn a
-plan (either the torch `DispatchPlan` or the fused path's plan header) into the numbers one wants
+plan (the host `RoutingPlan`'s own `stats()` or the fused path's plan header) into the numbers one wants
 on a dashboard: rows per rank, slices, padding, imbalance, bytes on the wire, and the roofline of
 the layer for the measured peaks.
 """

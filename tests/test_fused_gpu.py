@@ -183,6 +183,64 @@ def test_bad_send_order_entry_is_reported_not_dereferenced():
         fused.release_workspaces()  # the pass was abandoned half way: do not reuse this workspace
 
 
+def test_invalid_expert_id_is_reported_by_the_forward():
+    """An expert id outside [0, E): the sort records it, every kernel launched on the guessed slice count returns at
+    once, and the forward raises when it reads the pass's header (nothing is dereferenced, no wait runs out)."""
+    from chunked_ep_moe_b200.ops import fused
+
+    torch.manual_seed(0)
+    T, D, F, E, K, S = 64, 256, 256, 2, 2, 152  # a geometry no other test uses: the workspace is thrown away below
+    cfg = ChunkedMoEConfig(num_experts=E, top_k=K, slice_size=S, transport="nvshmem", expert_compute="fused",
+                           stripe_width=64)
+    x = torch.randn(T, D, device="cuda").bfloat16()
+    ids = torch.stack([torch.randperm(E, device="cuda")[:K] for _ in range(T)]).int().contiguous()
+    w = torch.rand(T, K, device="cuda")
+    w_up = (torch.randn(E, D, 2 * F, device="cuda") * 0.05).bfloat16()
+    w_down = (torch.randn(E, F, D, device="cuda") * 0.05).bfloat16()
+    try:
+        chunked_moe(x, ids, w, w_up, w_down, cfg, None)  # a good pass first: the next one launches on its slice count
+        bad = ids.clone()
+        bad[7, 1] = E
+        with pytest.raises(RuntimeError, match="index check failed"):
+            chunked_moe(x, bad, w, w_up, w_down, cfg, None)
+        torch.cuda.synchronize()
+        fused.check_status()  # the block was cleared when the error was raised
+    finally:
+        torch.cuda.synchronize()
+        fused.release_workspaces()  # the pass was abandoned half way: do not reuse this workspace
+
+
+def test_slice_count_guess_is_corrected_in_both_directions():
+    """The forward launches on the previous pass's slice count before it knows its own: passes that need more slices
+    than the one before, and fewer, must both match the oracle (the same workspace throughout)."""
+    gen = torch.Generator().manual_seed(9)
+    E, K, D, F, stripe, S = 4, 2, 256, 256, 64, 128
+    bf = lambda t: t.cuda().to(torch.bfloat16)
+    w_up = bf(torch.randn(E, D, 2 * F, generator=gen) / math.sqrt(D))
+    w_down = bf(torch.randn(E, F, D, generator=gen) / math.sqrt(F))
+    cfg = ChunkedMoEConfig(num_experts=E, top_k=K, slice_size=S, transport="nvshmem", expert_compute="fused",
+                           stripe_width=stripe)
+    T = 192  # 384 copies: 3 slices when balanced ...
+    for groups in ([96, 96, 96, 96], [100, 90, 102, 92], [96, 96, 96, 96]):
+        tokens = T
+        ids = _ids_with_groups(groups, K, E, gen)
+        assert ids.shape[0] == tokens
+        # ... and the second and third tensors below shrink the pass to 2 slices, then grow it back
+        for keep in (tokens, 100, tokens):
+            x, g = bf(torch.randn(keep, D, generator=gen)), bf(torch.randn(keep, D, generator=gen))
+            weights = (torch.rand(keep, K, generator=gen) + 0.1).cuda()
+            xs, ws = x.clone().requires_grad_(True), weights.clone().requires_grad_(True)
+            us, ds = w_up.clone().requires_grad_(True), w_down.clone().requires_grad_(True)
+            out = chunked_moe(xs, ids[:keep].cuda(), ws, us, ds, cfg, None)
+            out.backward(g)
+            torch.cuda.synchronize()
+            want = _oracle_dev(x, ids[:keep], weights, w_up, w_down, g, stripe)
+            _close(out.detach().cpu(), want["out"], f"out ({keep} tokens)")
+            _close(xs.grad.cpu(), want["dx"], f"dx ({keep} tokens)")
+            _close(us.grad.cpu(), want["dw_up"], f"dw_up ({keep} tokens)")
+            _close(ds.grad.cpu(), want["dw_down"], f"dw_down ({keep} tokens)")
+
+
 def test_gemm_whose_rows_never_arrive_gives_up_and_reports(monkeypatch):
     """The real swiglu kernel waiting for rows nobody sends: its bounded wait runs out, every warp unwinds promptly
     (the barrier waits watch the CTA's abort flag), later kernels of the pass return at once, the host raises."""

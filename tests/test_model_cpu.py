@@ -131,3 +131,22 @@ def test_two_ranks_give_the_gradients_of_one():
     for name, grad in one["experts"].items():  # [4 experts, ...] on one rank; [2 experts, ...] on each of two
         both = torch.cat([two[0]["experts"][name], two[1]["experts"][name]])
         assert torch.allclose(both, grad, rtol=1e-4, atol=1e-6), name
+
+
+def test_router_balancing_state_survives_a_bf16_cast():
+    """Casting the model to bf16 must leave the router's counts and selection bias in fp32: a bias of 0.5 still
+    moves by 1e-3 per step and counts in the thousands stay exact."""
+    from chunked_ep_moe_b200.models.deepseek_tiny import DeepSeekTinyConfig, Router
+
+    cfg = DeepSeekTinyConfig(vocab_size=64, d_model=32, n_layers=2, n_heads=2, head_dim=16, dense_ffn=64,
+                             num_experts=4, moe_ffn=32, top_k=2, shared_ffn=32, slice_size=16, transport="emulated",
+                             expert_compute="reference")
+    router = Router(cfg).to(dtype=torch.bfloat16)
+    assert router.weight.dtype == torch.bfloat16
+    assert router.routed_bias.dtype == torch.float32 and router.load_counts.dtype == torch.float32
+    router.routed_bias.fill_(0.5)
+    router.load_counts.copy_(torch.tensor([4097.0, 3.0, 2051.0, 1.0]))
+    assert router.load_counts.tolist() == [4097.0, 3.0, 2051.0, 1.0]
+    router.update_bias()
+    moved = (router.routed_bias - 0.5).abs()
+    assert torch.allclose(moved, torch.full_like(moved, cfg.bias_update_rate), rtol=1e-3), moved

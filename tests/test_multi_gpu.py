@@ -1,8 +1,10 @@
 """The fused NVLink path on real peers: one process per GPU over NCCL + CUDA IPC (needs >= 2 GPUs).
 
-Checks the fused layer and the NCCL baseline against the dense oracle, twice in a row through the
-same workspace (counters, credits and double buffers carry over), for balanced and skewed routing.
-NVLS is switched off for these short-lived ranks.
+Checks the fused layer (single-CTA and CTA-pair kernels, bf16 and fp8 wire) and the NCCL baseline against the
+dense oracle, twice in a row through the same workspace (counters, credits and double buffers carry over), for
+balanced and skewed routing; and the host-side peer-failure path: a rank that leaves between two steps, with
+nothing in flight, is named by the survivor's heartbeat before anything is launched. NVLS is switched off for
+these short-lived ranks.
 """
 
 import os
@@ -26,10 +28,10 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, out_dir, cases):
+def _worker(rank, world, port, out_dir, cases, pairs):
     import torch.distributed as dist
 
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", CEM_CTA_PAIRS=pairs)
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     result = {"ok": True, "errors": {}}
@@ -75,23 +77,81 @@ def _worker(rank, world, port, out_dir, cases):
     dist.destroy_process_group()
 
 
-def _run(world, cases):
+def _run(world, cases, pairs="0", worker=None):
     import torch.multiprocessing as mp
 
     with tempfile.TemporaryDirectory() as out_dir:
-        mp.spawn(_worker, args=(world, _free_port(), out_dir, cases), nprocs=world, join=True)
+        mp.spawn(worker or _worker, args=(world, _free_port(), out_dir, cases, pairs), nprocs=world, join=True)
         return [torch.load(os.path.join(out_dir, f"{r}.pt"), weights_only=False) for r in range(world)]
 
 
 CASES = [("uniform", 128, None), ("all_one", 64, None), ("rank0", 256, None), ("uniform", 128, "float8_e4m3fn")]
 
 
+@pytest.mark.parametrize("pairs", ["0", "1"], ids=["single", "pairs"])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_fused_layer_on_real_peers(world):
+def test_fused_layer_on_real_peers(world, pairs):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    for rank, res in enumerate(_run(world, CASES)):
+    for rank, res in enumerate(_run(world, CASES, pairs)):
         assert res["ok"], f"rank {rank} failed:\n{res.get('trace')}"
         for key, (err, finite) in res["errors"].items():
             limit = 0.08 if key[0][2] is not None else TOL
             assert finite and err <= limit, f"rank {rank} {key}: err {err:.4f}"
+
+
+def _leaver_worker(rank, world, port, out_dir, cases, pairs):
+    """Both ranks run step 0 of the fused layer to the end. Rank 1 then leaves (nothing of its own in flight, its
+    device idle); rank 0 asks the heartbeat before launching step 1 and must be told who is missing."""
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    result = {"ok": False}
+    try:
+        from chunked_ep_moe_b200 import ChunkedMoEConfig, chunked_moe
+        from chunked_ep_moe_b200.ops import fused
+        from chunked_ep_moe_b200.utils.health import PeerFailure, RankHealth
+
+        health = RankHealth(dist.distributed_c10d._get_default_store(), rank, world, timeout_s=3.0)
+        T, E, K, D, F, stripe = 96, 8, 2, 256, 256, 64
+        cfg = ChunkedMoEConfig(num_experts=E, top_k=K, slice_size=128, stripe_width=stripe, transport="nvshmem",
+                               expert_compute="fused")
+        x, ids, weights, w_up, w_down, g = moe_cases.setup(world, T, E, K, D, F, "uniform", seed=5)
+        bf = lambda t: t.to(torch.bfloat16)
+        sh = lambda t: moe_cases.shard(t, rank, world).cuda()
+        health.step_barrier(0)
+        xs = bf(sh(x)).requires_grad_(True)
+        out = chunked_moe(xs, sh(ids), sh(weights), bf(sh(w_up)), bf(sh(w_down)), cfg, None)
+        out.backward(bf(sh(g)))
+        fused.check_status()
+        torch.cuda.synchronize()
+        dist.barrier()  # step 0 is over on both ranks: no kernel, store or collective of either is in flight
+        torch.cuda.synchronize()
+        if rank == 1:
+            torch.save({"ok": True, "left": True}, os.path.join(out_dir, f"{rank}.pt"))
+            os._exit(0)  # leaves between steps, without a word
+        launches_before = fused.launches()
+        try:
+            health.step_barrier(1)
+            result = {"ok": False, "trace": "the heartbeat did not notice the missing rank"}
+        except PeerFailure as failure:
+            result = {"ok": True, "missing": failure.missing, "waited_s": failure.waited_s,
+                      "launched": fused.launches() - launches_before}
+    except Exception:
+        result = {"ok": False, "trace": traceback.format_exc()}
+    torch.save(result, os.path.join(out_dir, f"{rank}.pt"))
+    os._exit(0)  # the peer is gone: no collective teardown
+
+
+def test_peer_leaves_between_steps():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    left, survivor = None, None
+    res = _run(2, None, worker=_leaver_worker)
+    survivor, left = res[0], res[1]
+    assert left.get("left"), left
+    assert survivor["ok"], survivor.get("trace")
+    assert survivor["missing"] == [1] and survivor["launched"] == 0
+    assert survivor["waited_s"] < 10.0

@@ -1,4 +1,4 @@
-"""The extension's per-pass plan tables (the code the single-CTA plan kernel runs) vs the torch planner."""
+"""The extension's per-pass plan tables (the code the single-CTA plan kernel runs) vs the host planner."""
 
 import numpy as np
 import pytest
@@ -26,14 +26,14 @@ def _counts(P, L, tokens, top_k, skew, seed):
 
 @pytest.mark.parametrize("P,L,S", [(1, 4, 16), (2, 2, 4), (4, 2, 5), (8, 4, 24), (4, 8, 1000)])
 @pytest.mark.parametrize("skew", ["uniform", "all_one", "empty"])
-def test_tables_match_torch_planner(P, L, S, skew):
+def test_tables_match_host_planner(P, L, S, skew):
     _check_tables(P, L, S, 16, 2, skew, seed=P * 100 + L)
 
 
 @settings(max_examples=40, deadline=None)
 @given(P=st.integers(1, 6), L=st.integers(1, 5), S=st.integers(1, 40), tokens=st.integers(1, 24),
        top_k=st.integers(1, 3), skew=st.sampled_from(["uniform", "all_one", "empty"]), seed=st.integers(0, 10**6))
-def test_tables_match_torch_planner_fuzzed(P, L, S, tokens, top_k, skew, seed):
+def test_tables_match_host_planner_fuzzed(P, L, S, tokens, top_k, skew, seed):
     """Arbitrary small geometries: single rows, S = 1, slices longer than the whole stream, experts with nothing."""
     _check_tables(P, L, S, tokens, min(top_k, P * L), skew, seed)
 
@@ -45,31 +45,30 @@ def _check_tables(P, L, S, tokens, top_k, skew, seed):
     lay = ext.plan_layout(P, L, S, max_slices)
     n = P * L
     for me in range(P):
-        ref = plan_lib.plan_from_counts(orders[me], counts, S, me)
+        ref = plan_lib.RoutingPlan(orders[me], counts, S, me)
         tab = ext.plan_build_host(counts.to(torch.int32).contiguous(), S, max_slices, me).numpy()
         assert tab[0] == ref.num_slices
-        assert tab[1] == int(plan_lib.stream_rows(ref)[me])
+        assert tab[1] == int(ref.rows[me])
         assert tab[5] == tokens * top_k
         sl = lambda key, cnt: tab[lay[key]: lay[key] + cnt]
-        np.testing.assert_array_equal(sl("send_start", n), ref.send_start[me].numpy())
-        np.testing.assert_array_equal(sl("seg_start", n), ref.recv_start[:, :, me].reshape(-1).numpy())
-        np.testing.assert_array_equal(sl("seg_size", n), ref.counts[me].reshape(-1).numpy())
-        np.testing.assert_array_equal(sl("in_start", n), ref.recv_start[me].transpose(0, 1).reshape(-1).numpy())
-        np.testing.assert_array_equal(sl("in_size", n), ref.counts[:, me, :].reshape(-1).numpy())
-        np.testing.assert_array_equal(sl("src_send_start", n),
-                                      ref.send_start.reshape(P, P, L)[:, me, :].reshape(-1).numpy())
-        np.testing.assert_array_equal(sl("expert_start", L), ref.expert_start[me].numpy())
-        np.testing.assert_array_equal(sl("expert_rows", L), ref.expert_rows[me].numpy())
+        np.testing.assert_array_equal(sl("send_start", n), ref.send_begin[me].reshape(-1))
+        np.testing.assert_array_equal(sl("seg_start", n), ref.stream_begin[:, :, me].reshape(-1))
+        np.testing.assert_array_equal(sl("seg_size", n), ref.counts[me].reshape(-1))
+        np.testing.assert_array_equal(sl("in_start", n), ref.stream_begin[me].T.reshape(-1))
+        np.testing.assert_array_equal(sl("in_size", n), ref.counts[:, me, :].reshape(-1))
+        np.testing.assert_array_equal(sl("src_send_start", n), ref.send_begin[:, me, :].reshape(-1))
+        np.testing.assert_array_equal(sl("expert_start", L), ref.expert_begin[me])
+        np.testing.assert_array_equal(sl("expert_rows", L), ref.expert_rows[me])
         seen_final = np.zeros(L, dtype=np.int64)
         for j in range(max_slices):
-            d = plan_lib.dispatch_args(ref, j, S)
-            groups = plan_lib.slice_group_sizes(ref, j, S).numpy()
+            d = ref.dispatch_spec(j)
+            groups = ref.group_rows(j)
             put = tab[lay["put"] + 4 * n * j: lay["put"] + 4 * n * (j + 1)].reshape(n, 4)
             if j < ref.num_slices:
-                np.testing.assert_array_equal(put[:, 1], d.send_sizes.numpy())
+                np.testing.assert_array_equal(put[:, 1], d.send_rows)
                 live = put[:, 1] > 0
-                np.testing.assert_array_equal(put[live, 0], d.input_offsets.numpy()[live])
-                np.testing.assert_array_equal(put[live, 2], d.output_offsets.numpy()[live])
+                np.testing.assert_array_equal(put[live, 0], d.src_offset[live])
+                np.testing.assert_array_equal(put[live, 2], d.dst_offset[live])
                 chunks = -(-put[:, 1] // lay["put_chunk_rows"])
                 np.testing.assert_array_equal(put[:, 3], np.cumsum(chunks) - chunks)
                 assert tab[lay["num_chunks"] + j] == chunks.sum()
@@ -98,7 +97,7 @@ def _check_tables(P, L, S, tokens, top_k, skew, seed):
             num_g = tab[lay["num_gtiles"] + j]
             gt = tab[lay["gtiles"] + 4 * lay["max_gtiles"] * j:][: 4 * num_g].reshape(num_g, 4)
             for e, row0, nrows, flags in gt:
-                es, er = int(ref.expert_start[me][e]), int(ref.expert_rows[me][e])
+                es, er = int(ref.expert_begin[me][e]), int(ref.expert_rows[me][e])
                 if nrows == 0:
                     assert j == 0 and er == 0 and flags == 3
                 else:

@@ -58,6 +58,21 @@ def test_noalloc_expert_sort_matches_the_regular_entry_point():
         assert torch.equal(order, want_order)
         assert torch.equal(inv, want_inv)
         assert torch.equal(counts, want_counts)
+    world.close()
+    # The corners of the built-in scratch: the largest problem the entry point accepts (524288 ids, 1024 experts:
+    # the only case that touches the array's last entries) and the smallest (one id).
+    big_cfg = ChunkedMoEConfig(num_experts=1024, top_k=8, slice_size=256, transport="nvshmem",
+                               expert_compute="fused", stripe_width=64)
+    world = LockstepWorld(big_cfg, 1, 256, 256, 524288 // 8)
+    for n in (524288, 1):
+        ids = torch.randint(0, 1024, (n,), generator=gen, dtype=torch.int32).cuda()
+        order = torch.full((n,), -1, dtype=torch.int32, device="cuda")
+        inv = torch.full((n,), -1, dtype=torch.int32, device="cuda")
+        counts = torch.full((1024,), -1, dtype=torch.int32, device="cuda")
+        assert fn(ids.data_ptr(), n, 1024, order.data_ptr(), inv.data_ptr(), counts.data_ptr(), stream) == 0
+        torch.cuda.synchronize()
+        want_order, want_inv, want_counts = _regular_sort(world.ranks[0], ids, 1024)
+        assert torch.equal(order, want_order) and torch.equal(inv, want_inv) and torch.equal(counts, want_counts)
     # sizes beyond the built-in scratch are refused, not truncated
     ids = torch.zeros(8, dtype=torch.int32, device="cuda")
     out = torch.zeros(8, dtype=torch.int32, device="cuda")
