@@ -141,6 +141,43 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+class NvlinkCounter:
+    """NVLink payload bytes this GPU sent and received, from NVML's per-device throughput counters (read-only).
+
+    Used to set the bytes the fused kernels really put on the wire against the algorithmic bytes of the layer. Any
+    failure (no NVML, counters not exposed) yields None: the number is evidence, never a dependency.
+    """
+
+    TX, RX = 138, 139  # NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_TX / _RX, KiB since the driver was loaded
+
+    def __init__(self, index: int):
+        self.handle = None
+        try:
+            import pynvml
+
+            import torch
+
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByUUID("GPU-" + str(torch.cuda.get_device_properties(index).uuid))
+        except Exception:  # noqa: BLE001
+            self.handle = None
+
+    def read(self):
+        if self.handle is None:
+            return None
+        try:
+            vals = self.nvml.nvmlDeviceGetFieldValues(self.handle, [(self.TX, 0xFFFFFFFF), (self.RX, 0xFFFFFFFF)])
+            out = []
+            for v in vals:
+                if v.nvmlReturn != 0:
+                    return None
+                out.append(int(v.value.ullVal) * 1024)
+            return tuple(out)
+        except Exception:  # noqa: BLE001
+            return None
+
+
 def make_routing(gen, tokens, experts, top_k, skew, device):
     import torch
 
@@ -287,14 +324,17 @@ def main():
 
     sampler = ClockSampler(local_rank)
     sampler.start()
+    nvlink = NvlinkCounter(local_rank)
     l0 = launches()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync_all()
+    link0 = nvlink.read()
     start.record()
     for _ in range(args.steps):
         step(x_d.detach(), ids_d, weights_d.detach())
     stop.record()
     sync_all()
+    link1 = nvlink.read()
     ms = start.elapsed_time(stop) / args.steps
     total_launches = launches() - l0
     n_launch = total_launches // max(args.steps, 1)
@@ -430,6 +470,14 @@ def main():
                           "value": world * T / (base_ms / 1e3)} if base_ms else
                          ({"unavailable": base_note or "not run"} if fused else None)),
             "e2e": e2e,
+            # rank 0's NVLink payload per step from NVML's counters, next to what the layer has to move: five row
+            # streams (x; x, g; y; dx) of T*K rows of D bf16 values (the dispatch streams at the wire dtype), of which
+            # (N-1)/N leave the GPU with uniform routing
+            "nvlink": ({"tx_bytes_per_step": (link1[0] - link0[0]) / args.steps,
+                        "rx_bytes_per_step": (link1[1] - link0[1]) / args.steps,
+                        "algorithmic_bytes_per_step_each_way":
+                            T * K * D * (2 * 2 + 3 * (1 if args.comm_dtype else 2)) * (world - 1) / world}
+                       if (link0 and link1 and world > 1) else None),
             "gpu_launches": int(total_launches),  # this repo's kernels launched inside the timed region (all steps)
             "gpu_launches_per_step": int(n_launch),
             "host": affinity_note,

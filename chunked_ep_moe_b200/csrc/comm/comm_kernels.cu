@@ -167,12 +167,20 @@ __global__ void slice_done_kernel(uint32_t* const* peer_credit, int num_ranks, i
   if (threadIdx.x < num_ranks) st_release_sys(peer_credit[threadIdx.x] + me, seq + 1);
 }
 
-__global__ void pass_begin_kernel(const int* plan, PlanLayout lay, uint32_t* expected_total, uint32_t* pass_base) {
+__global__ void pass_begin_kernel(const int* plan, PlanLayout lay, uint32_t* expected_total, uint32_t* pass_base,
+                                  uint32_t* ready_total, uint32_t* ready_base) {
   const int n = lay.P * lay.L;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const uint32_t base = expected_total[i];
     pass_base[i] = base;
     expected_total[i] = base + static_cast<uint32_t>(plan[lay.off_in_size + i]);
+  }
+  if (ready_total != nullptr) {
+    for (int l = threadIdx.x; l < lay.L; l += blockDim.x) {
+      const uint32_t base = ready_total[l];
+      ready_base[l] = base;
+      ready_total[l] = base + static_cast<uint32_t>(plan[lay.off_expert_rows + l]);
+    }
   }
 }
 
@@ -213,16 +221,16 @@ __global__ void __launch_bounds__(256) combine_reduce_kernel(const CombineParams
   }
 }
 
-__device__ __forceinline__ void dequant_rows(const uint8_t* q, const float* scales, __nv_bfloat16* out, int rows,
-                                             int hidden) {
-  const int units = hidden >> 3;  // 8 values per thread step
-  const size_t total = static_cast<size_t>(rows) * units;
-  for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total;
-       idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const size_t row = idx / units;
-    const int u = static_cast<int>(idx - row * units);
-    const uint2 raw = *reinterpret_cast<const uint2*>(q + row * hidden + static_cast<size_t>(u) * 8);
-    const float scale = scales[row * (hidden >> 7) + (u >> 4)];
+// Expands one e4m3 row with its 1x128 block scales into bf16; the CTA's threads stride over 8-value units.
+__device__ __forceinline__ void dequant_row(const uint8_t* q, const float* scales, __nv_bfloat16* out, int row,
+                                            int hidden) {
+  const int units = hidden >> 3;
+  const uint8_t* qrow = q + static_cast<size_t>(row) * hidden;
+  const float* srow = scales + static_cast<size_t>(row) * (hidden >> 7);
+  __nv_bfloat16* orow = out + static_cast<size_t>(row) * hidden;
+  for (int u = threadIdx.x; u < units; u += blockDim.x) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(qrow + static_cast<size_t>(u) * 8);
+    const float scale = srow[u >> 4];
     float v[8];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -231,7 +239,7 @@ __device__ __forceinline__ void dequant_rows(const uint8_t* q, const float* scal
       v[i] = __half2float(*reinterpret_cast<const __half*>(&h0)) * scale;
       v[4 + i] = __half2float(*reinterpret_cast<const __half*>(&h1)) * scale;
     }
-    *reinterpret_cast<int4*>(out + row * hidden + static_cast<size_t>(u) * 8) =
+    *reinterpret_cast<int4*>(orow + static_cast<size_t>(u) * 8) =
         make_int4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
   }
 }
@@ -241,22 +249,36 @@ __global__ void __launch_bounds__(256) dequant_slice_kernel(const DequantParams 
   if (threadIdx.x == 0) s_abort = (p.status != nullptr && p.status->code != 0) ? 1 : 0;
   __syncthreads();
   if (s_abort) return;
-  const int n = p.lay.P * p.lay.L;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int through = plan_clip((p.slice + 1) * p.lay.S - p.plan[p.lay.off_in_start + i], 0,
-                                  p.plan[p.lay.off_in_size + i]);
-    const uint32_t target = p.pass_base[i] + static_cast<uint32_t>(through);
-    uint32_t seen = 0;
-    if (!spin_until_reached(p.arrive + i, target, p.spin_limit, &seen)) {
-      report_status(p.status, kStatusArrivalTimeout, kKernelPut, 1, p.slice, i, target, seen);
-      s_abort = 1;
+  const int lo = p.slice * p.lay.S, hi = lo + p.lay.S;
+  for (int l = 0; l < p.lay.L; ++l) {
+    const int es = p.plan[p.lay.off_expert_start + l], er = p.plan[p.lay.off_expert_rows + l];
+    const int first = plan_clip(lo, es, es + er), last = plan_clip(hi, es, es + er);
+    if (last <= first) continue;
+    // This expert's rows of the slice have arrived from every source (thread s watches source s).
+    if (threadIdx.x < p.lay.P) {
+      const int i = threadIdx.x * p.lay.L + l;
+      const int through = plan_clip(hi - p.plan[p.lay.off_in_start + i], 0, p.plan[p.lay.off_in_size + i]);
+      const uint32_t target = p.pass_base[i] + static_cast<uint32_t>(through);
+      uint32_t seen = 0;
+      if (!spin_until_reached(p.arrive + i, target, p.spin_limit, &seen)) {
+        report_status(p.status, kStatusArrivalTimeout, kKernelPut, 1, p.slice, i, target, seen);
+        s_abort = 1;
+      }
+    }
+    __syncthreads();
+    if (s_abort) return;
+    // Slice rows [first - lo, last - lo); this CTA takes every gridDim.x-th of them.
+    uint32_t mine = 0;
+    for (int r = first - lo + blockIdx.x; r < last - lo; r += gridDim.x, ++mine) {
+      dequant_row(p.xq, p.xs, p.x, r, p.hidden);
+      if (p.gq != nullptr) dequant_row(p.gq, p.gs, p.g, r, p.hidden);
+    }
+    __syncthreads();  // all of this CTA's stores for the expert are issued before one thread releases them
+    if (threadIdx.x == 0 && mine > 0) {
+      __threadfence();
+      atomicAdd(p.ready + l, mine);
     }
   }
-  __syncthreads();
-  if (s_abort) return;
-  const int rows = plan_clip(p.plan[1] - p.slice * p.lay.S, 0, p.lay.S);
-  dequant_rows(p.xq, p.xs, p.x, rows, p.hidden);
-  if (p.gq != nullptr) dequant_rows(p.gq, p.gs, p.g, rows, p.hidden);
 }
 
 __global__ void wait_probe_kernel(const uint32_t* flag, uint32_t target, uint32_t spin_limit, StatusBlock* status) {
@@ -276,8 +298,8 @@ void launch_slice_done(uint32_t* const* peer_credit, int num_ranks, int me, uint
 }
 
 void launch_pass_begin(const int* plan, PlanLayout lay, uint32_t* expected_total, uint32_t* pass_base,
-                       cudaStream_t stream) {
-  pass_begin_kernel<<<1, 256, 0, stream>>>(plan, lay, expected_total, pass_base);
+                       uint32_t* ready_total, uint32_t* ready_base, cudaStream_t stream) {
+  pass_begin_kernel<<<1, 256, 0, stream>>>(plan, lay, expected_total, pass_base, ready_total, ready_base);
 }
 
 void launch_combine_reduce(const CombineParams& p, cudaStream_t stream) {
@@ -287,7 +309,10 @@ void launch_combine_reduce(const CombineParams& p, cudaStream_t stream) {
 }
 
 void launch_dequant_slice(const DequantParams& p, cudaStream_t stream) {
-  dequant_slice_kernel<<<592, 256, 0, stream>>>(p);
+  // Every CTA visits every expert of the slice and waits for its arrival, so ALL CTAs must be resident at once for
+  // an expert's rows to be released while later experts are still arriving: 72 CTAs of 256 threads fit on the dozen
+  // SMs the up-projection GEMM leaves free on the fp8 wire (8 such CTAs per SM).
+  dequant_slice_kernel<<<72, 256, 0, stream>>>(p);
 }
 
 void launch_wait_probe(const uint32_t* flag, uint32_t target, uint32_t spin_limit, StatusBlock* status,

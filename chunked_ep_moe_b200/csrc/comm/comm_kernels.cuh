@@ -40,9 +40,11 @@ void launch_dispatch_put(const PutParams& p, int grid, cudaStream_t stream);
 // Tells every sender that this rank has finished reading the slice buffers of sequence `seq`.
 void launch_slice_done(uint32_t* const* peer_credit, int num_ranks, int me, uint32_t seq, cudaStream_t stream);
 
-// Snapshot of the arrival-counter targets at the start of a pass: base = total; total += rows expected.
+// Snapshot of the counter targets at the start of a pass: base = total; total += rows expected. `expected_total` /
+// `pass_base` are the [P*L] arrival counters' totals and bases; `ready_total` / `ready_base` ([L], may be null) the
+// same for the per-expert "rows expanded" counters of the fp8 wire.
 void launch_pass_begin(const int* plan, PlanLayout lay, uint32_t* expected_total, uint32_t* pass_base,
-                       cudaStream_t stream);
+                       uint32_t* ready_total, uint32_t* ready_base, cudaStream_t stream);
 
 struct CombineParams {
   const __nv_bfloat16* rows;  // [T*K, D] returned rows in send order
@@ -59,9 +61,11 @@ struct CombineParams {
 
 void launch_combine_reduce(const CombineParams& p, cudaStream_t stream);
 
-// Receiver-side expansion of an arrived fp8 slice (e4m3 + one fp32 scale per 128 columns) into the bf16
-// slice buffer the GEMMs read. The kernel is the slice's first consumer, so it acquires the arrival
-// counters of every (source, expert) segment of the slice itself before it reads anything.
+// Receiver-side expansion of arrived fp8 rows (e4m3 + one fp32 scale per 128 columns) into the bf16 slice buffer
+// the GEMMs read, expert by expert: the kernel acquires the arrival counters of ONE expert's segments, expands that
+// expert's rows, releases the row count to the expert's `ready` counter, and goes on to the next expert. The
+// up-projection GEMM's producer waits on `ready`, so expansion and transfer of later experts overlap the tiles of
+// earlier ones, as arrival does on the bf16 wire.
 struct DequantParams {
   const int* plan;
   PlanLayout lay;
@@ -75,6 +79,7 @@ struct DequantParams {
   const uint8_t* gq;          // backward: the output gradient's slice, or null
   const float* gs;
   __nv_bfloat16* g;
+  uint32_t* ready;            // [L] cumulative rows of local expert l expanded so far (local counter, only grows)
   uint32_t spin_limit;
   StatusBlock* status;
 };

@@ -73,7 +73,20 @@ __device__ __forceinline__ void resolve_source(const GemmParams& p, int g, int g
 // written through the generic proxy and TMA reads them next. Returns false on expiry (status recorded, abort set).
 __device__ __forceinline__ bool wait_expert_rows(const GemmParams& p, int g, int lane, volatile int* abort_flag) {
   bool ok = true;
-  if (lane < p.lay.P) {
+  if (p.ready != nullptr) {
+    // fp8 wire: the expansion kernel releases an expert's rows (bf16, local) once they have arrived and been expanded.
+    if (lane == 0) {
+      const int through = plan_clip((p.slice + 1) * p.lay.S - p.plan[p.lay.off_expert_start + g], 0,
+                                    p.plan[p.lay.off_expert_rows + g]);
+      const uint32_t target = p.ready_base[g] + static_cast<uint32_t>(through);
+      uint32_t seen = 0;
+      ok = spin_until_reached(p.ready + g, target, p.spin_limit, &seen);
+      if (!ok) {
+        report_status(p.status, kStatusArrivalTimeout, kKernelGemm, kModeSwiglu, p.slice, 10000 + g, target, seen);
+        *abort_flag = 1;
+      }
+    }
+  } else if (lane < p.lay.P) {
     const int i = lane * p.lay.L + g;
     const int through = plan_clip((p.slice + 1) * p.lay.S - p.plan[p.lay.off_in_start + i], 0,
                                   p.plan[p.lay.off_in_size + i]);

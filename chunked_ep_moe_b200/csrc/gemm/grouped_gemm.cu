@@ -142,7 +142,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
         const Tile tl = nxt;
         if (t + static_cast<int>(gridDim.x) < num_tiles) nxt = decode_tile<MODE>(p, t + static_cast<int>(gridDim.x), num_entries);
         if constexpr (MODE == kModeSwiglu) {
-          if (p.arrive != nullptr && tl.g != waited_expert) {
+          if ((p.arrive != nullptr || p.ready != nullptr) && tl.g != waited_expert) {
             if (!wait_expert_rows(p, tl.g, lane, abort_flag)) break;
             waited_expert = tl.g;
           }

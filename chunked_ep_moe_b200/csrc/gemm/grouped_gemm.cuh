@@ -61,6 +61,9 @@ struct GemmParams {
   // --- arrival flags (swiglu consumer) -----------------------------------------------------
   const uint32_t* arrive;     // [P*L] cumulative rows received per (source, local expert); null = no wait
   const uint32_t* pass_base;  // [P*L] value of `arrive` when this pass began
+  // fp8 wire: rows are usable once the expansion kernel has released them, per local expert (replaces `arrive`)
+  const uint32_t* ready;       // [L] cumulative rows expanded per local expert; null = not used
+  const uint32_t* ready_base;  // [L] value of `ready` when this pass began
   // --- row-wise outputs / inputs (leading dims in elements) -----------------------------------
   __nv_bfloat16* out0;        // swiglu: act [S,F]; down_dw: dy [S,D]; dswiglu: dh [S,2F]
   __nv_bfloat16* out1;        // swiglu: h [S,2F] or null

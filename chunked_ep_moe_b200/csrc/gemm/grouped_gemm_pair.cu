@@ -181,7 +181,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
         const Tile tl = nxt;
         if (t + tile_step < num_tiles) nxt = decode_pair_tile<MODE>(p, t + tile_step, num_entries, rank);
         if constexpr (MODE == kModeSwiglu) {
-          if (p.arrive != nullptr && tl.g != waited_expert) {
+          if ((p.arrive != nullptr || p.ready != nullptr) && tl.g != waited_expert) {
             if (!wait_expert_rows(p, tl.g, lane, abort_flag)) break;
             waited_expert = tl.g;
           }

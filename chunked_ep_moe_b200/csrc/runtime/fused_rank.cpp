@@ -15,6 +15,8 @@ namespace cem {
 
 namespace {
 
+constexpr int kExpandSms = 12;  // SMs the up-projection GEMM leaves to the fp8 expansion kernel
+
 inline void cuda_check(cudaError_t err, const char* what) {
   if (err != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(err));
 }
@@ -109,6 +111,9 @@ FusedRank::FusedRank(int P, int L, int me, int S, int D, int F, int K, int strip
   carry_up_ = torch::zeros({2, D, 2 * F}, f32);
   carry_down_ = torch::zeros({2, F, D}, f32);
   pass_base_ = torch::zeros({P * L}, i32);
+  ready_ = torch::zeros({L}, i32);
+  ready_base_ = torch::zeros({L}, i32);
+  ready_total_ = torch::zeros({L}, i32);
   expected_total_ = torch::zeros({P * L}, i32);
   status_ = torch::zeros({8}, i32);
   my_counts_ = torch::zeros({P * L}, i32);
@@ -156,10 +161,15 @@ FusedRank::FusedRank(int P, int L, int me, int S, int D, int F, int K, int strip
   }
 
   if (use_comm_stream_) {
-    cuda_check(cudaStreamCreateWithFlags(&comm_stream_, cudaStreamNonBlocking), "comm stream");
+    // The put and expansion kernels feed kernels that wait for them: their blocks go first when SMs free up.
+    int prio_low = 0, prio_high = 0;
+    cuda_check(cudaDeviceGetStreamPriorityRange(&prio_low, &prio_high), "stream priority range");
+    cuda_check(cudaStreamCreateWithPriority(&comm_stream_, cudaStreamNonBlocking, prio_high), "comm stream");
     cuda_check(cudaStreamCreateWithFlags(&aux_stream_, cudaStreamNonBlocking), "aux stream");
     for (int q = 0; q < 2; ++q) cuda_check(cudaStreamCreateWithFlags(&chain_[q], cudaStreamNonBlocking), "chain stream");
+    if (fp8_) cuda_check(cudaStreamCreateWithPriority(&expand_stream_, cudaStreamNonBlocking, prio_high), "expand stream");
   }
+  for (int i = 0; i < 4; ++i) cuda_check(cudaEventCreateWithFlags(&ev_expand_[i], cudaEventDisableTiming), "event");
   for (int q = 0; q < 2; ++q)
     for (cudaEvent_t* e : {&ev_down_[q], &ev_dd_[q], &ev_ds_[q], &ev_dx_[q], &ev_tgd_[q], &ev_tgu_[q]})
       cuda_check(cudaEventCreateWithFlags(e, cudaEventDisableTiming), "event");
@@ -176,6 +186,9 @@ FusedRank::FusedRank(int P, int L, int me, int S, int D, int F, int K, int strip
 FusedRank::~FusedRank() {
   if (comm_stream_) cudaStreamDestroy(comm_stream_);
   if (aux_stream_) cudaStreamDestroy(aux_stream_);
+  if (expand_stream_) cudaStreamDestroy(expand_stream_);
+  for (int i = 0; i < 4; ++i)
+    if (ev_expand_[i]) cudaEventDestroy(ev_expand_[i]);
   for (int q = 0; q < 2; ++q) {
     if (chain_[q]) cudaStreamDestroy(chain_[q]);
     for (cudaEvent_t e : {ev_down_[q], ev_dd_[q], ev_ds_[q], ev_dx_[q], ev_tgd_[q], ev_tgu_[q]})
@@ -329,7 +342,9 @@ int64_t FusedRank::begin_backward(torch::Tensor plan, int64_t known_slices, int6
     cur_rows_ = host_header_[5];
   }
   launch_pass_begin(plan.data_ptr<int>(), lay_, reinterpret_cast<uint32_t*>(expected_total_.data_ptr()),
-                    reinterpret_cast<uint32_t*>(pass_base_.data_ptr()), st);
+                    reinterpret_cast<uint32_t*>(pass_base_.data_ptr()),
+                    fp8_ ? reinterpret_cast<uint32_t*>(ready_total_.data_ptr()) : nullptr,
+                    fp8_ ? reinterpret_cast<uint32_t*>(ready_base_.data_ptr()) : nullptr, st);
   ++launches_;
   ret_target_ += static_cast<uint32_t>(cur_rows_) * static_cast<uint32_t>(D_ / kBlockN);
   if (use_comm_stream_) cuda_check(cudaEventRecord(ev_pass_, st), "event record");
@@ -379,6 +394,14 @@ void FusedRank::put(int64_t j, torch::Tensor plan, torch::Tensor order, torch::T
   launch_dispatch_put(p, put_blocks_, st);
   ++launches_;
   if (use_comm_stream_) cuda_check(cudaEventRecord(ev_put_[j % 4], comm_stream_), "event record");
+  if (fp8_ && use_comm_stream_) {
+    // The expansion of slice j is issued together with its put, one slice ahead of the GEMMs: it waits for arrivals
+    // expert by expert while slice j-1 computes. It may overwrite the bf16 slice buffer once slice j-2 is done with it.
+    if (j == 0) cuda_check(cudaStreamWaitEvent(expand_stream_, ev_pass_, 0), "wait pass event");
+    if (j >= 2) cuda_check(cudaStreamWaitEvent(expand_stream_, ev_done_[(j - 2) % 4], 0), "wait slice event");
+    dequant(plan.data_ptr<int>(), static_cast<int>(j), static_cast<int>(p.seq & 1u), g.has_value(), expand_stream_);
+    cuda_check(cudaEventRecord(ev_expand_[j % 4], expand_stream_), "event record");
+  }
 }
 
 GemmParams FusedRank::base_params(const int* plan, int j) const {
@@ -427,6 +450,7 @@ void FusedRank::dequant(const int* plan, int j, int b, bool with_g, cudaStream_t
     d.gs = reinterpret_cast<const float*>(arena_ + arena_lay_.gs) + rows_off * (D_ / 128);
     d.g = reinterpret_cast<__nv_bfloat16*>(arena_ + arena_lay_.gbuf) + rows_off * D_;
   }
+  d.ready = reinterpret_cast<uint32_t*>(ready_.data_ptr());
   d.spin_limit = spin_limit_;
   d.status = reinterpret_cast<StatusBlock*>(status_.data_ptr());
   launch_dequant_slice(d, st);
@@ -446,14 +470,15 @@ void FusedRank::set_pipeline_counters(c10::optional<torch::Tensor> counters) {
 }
 
 void FusedRank::launch_gemm(int mode, const GemmParams& p0, const CUtensorMap& a, const CUtensorMap& b,
-                            cudaStream_t st, const CUtensorMap* c) {
+                            cudaStream_t st, const CUtensorMap* c, int spare_sms) {
   GemmParams p = p0;
   if (prof_.defined())
     p.prof = reinterpret_cast<unsigned long long*>(prof_.data_ptr<int64_t>()) +
              static_cast<size_t>(mode) * prof_.size(1) * kProfSlots;
   const CUtensorMap& out = c != nullptr ? *c : a;
-  if (mode == kModeTgmm ? tgmm_pairs_ : cta_pairs_) launch_grouped_gemm_pair(mode, p, a, b, out, num_sms_, st);
-  else launch_grouped_gemm(mode, p, a, b, out, num_sms_, st);
+  const int grid = std::max(2, num_sms_ - spare_sms);
+  if (mode == kModeTgmm ? tgmm_pairs_ : cta_pairs_) launch_grouped_gemm_pair(mode, p, a, b, out, grid, st);
+  else launch_grouped_gemm(mode, p, a, b, out, grid, st);
   ++launches_;
 }
 
@@ -487,7 +512,7 @@ void FusedRank::compute_forward(int64_t j, torch::Tensor plan, torch::Tensor w_u
   const uint32_t seq = seq_ + static_cast<uint32_t>(j);
   const int b = static_cast<int>(seq & 1u);
   const int* pl = plan.data_ptr<int>();
-  if (fp8_) dequant(pl, static_cast<int>(j), b, /*with_g=*/false, st);
+  if (fp8_ && !async) dequant(pl, static_cast<int>(j), b, /*with_g=*/false, st);  // lockstep: every put is done
   {
     GemmParams p = base_params(pl, static_cast<int>(j));
     p.n_tiles = 2 * F_ / kBlockN;
@@ -495,11 +520,19 @@ void FusedRank::compute_forward(int64_t j, torch::Tensor plan, torch::Tensor w_u
     p.b_group_rows = D_;
     p.arrive = fp8_ ? nullptr : reinterpret_cast<const uint32_t*>(arena_ + arena_lay_.arrive);
     p.pass_base = reinterpret_cast<const uint32_t*>(pass_base_.data_ptr());
+    p.ready = fp8_ ? reinterpret_cast<const uint32_t*>(ready_.data_ptr()) : nullptr;
+    p.ready_base = reinterpret_cast<const uint32_t*>(ready_base_.data_ptr());
     p.out0 = reinterpret_cast<__nv_bfloat16*>(act_[q].data_ptr());
     p.ld0 = F_;
     p.out1 = nullptr;
     p.ld1 = 2 * F_;
-    launch_gemm(kModeSwiglu, p, map_x_k_[b], weight_map(w_up, 64, cta_pairs_ ? 2 : 4), st);
+    // fp8 wire: this kernel waits (in its producer warp) for the expansion kernel of the same slice. A persistent CTA
+    // takes all of an SM's shared memory, so nothing else can start beside it: the kernel leaves a few SMs free for the
+    // expansion kernel, and it only starts once the expansion of the PREVIOUS slice has finished, so that at most one
+    // kernel is ever waiting for an expansion that still needs SMs.
+    if (fp8_ && async && j >= 1) cuda_check(cudaStreamWaitEvent(st, ev_expand_[(j - 1) % 4], 0), "wait expansion");
+    launch_gemm(kModeSwiglu, p, map_x_k_[b], weight_map(w_up, 64, cta_pairs_ ? 2 : 4), st, nullptr,
+                fp8_ && async ? kExpandSms : 0);
   }
   {
     GemmParams p = base_params(pl, static_cast<int>(j));
@@ -540,7 +573,7 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
   const int* pl = plan.data_ptr<int>();
   const int par = static_cast<int>(j & 1);
   const int dwp_tiles = D_ / kBlockN;
-  if (fp8_) dequant(pl, static_cast<int>(j), b, /*with_g=*/true, st);
+  if (fp8_ && !async) dequant(pl, static_cast<int>(j), b, /*with_g=*/true, st);  // lockstep: every put is done
   {  // remat: act and h
     GemmParams p = base_params(pl, static_cast<int>(j));
     p.n_tiles = 2 * F_ / kBlockN;
@@ -548,11 +581,19 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
     p.b_group_rows = D_;
     p.arrive = fp8_ ? nullptr : reinterpret_cast<const uint32_t*>(arena_ + arena_lay_.arrive);
     p.pass_base = reinterpret_cast<const uint32_t*>(pass_base_.data_ptr());
+    p.ready = fp8_ ? reinterpret_cast<const uint32_t*>(ready_.data_ptr()) : nullptr;
+    p.ready_base = reinterpret_cast<const uint32_t*>(ready_base_.data_ptr());
     p.out0 = reinterpret_cast<__nv_bfloat16*>(act_[q].data_ptr());
     p.ld0 = F_;
     p.out1 = reinterpret_cast<__nv_bfloat16*>(h_[q].data_ptr());
     p.ld1 = 2 * F_;
-    launch_gemm(kModeSwiglu, p, map_x_k_[b], weight_map(w_up, 64, cta_pairs_ ? 2 : 4), st);
+    // fp8 wire: this kernel waits (in its producer warp) for the expansion kernel of the same slice. A persistent CTA
+    // takes all of an SM's shared memory, so nothing else can start beside it: the kernel leaves a few SMs free for the
+    // expansion kernel, and it only starts once the expansion of the PREVIOUS slice has finished, so that at most one
+    // kernel is ever waiting for an expansion that still needs SMs.
+    if (fp8_ && async && j >= 1) cuda_check(cudaStreamWaitEvent(st, ev_expand_[(j - 1) % 4], 0), "wait expansion");
+    launch_gemm(kModeSwiglu, p, map_x_k_[b], weight_map(w_up, 64, cta_pairs_ ? 2 : 4), st, nullptr,
+                fp8_ && async ? kExpandSms : 0);
   }
   {  // remat of y, folded into d_weight partials; dy = w * g
     GemmParams p = base_params(pl, static_cast<int>(j));
@@ -632,6 +673,7 @@ void FusedRank::join_streams(bool backward) {
   if (!use_comm_stream_ || cur_slices_ <= 0) return;
   cudaStream_t st = current_stream();
   cuda_check(cudaStreamWaitEvent(st, ev_done_[(cur_slices_ - 1) % 4], 0), "join aux stream");
+  if (fp8_) cuda_check(cudaStreamWaitEvent(st, ev_expand_[(cur_slices_ - 1) % 4], 0), "join expand stream");
   if (backward) {
     cuda_check(cudaStreamWaitEvent(st, ev_dx_[(cur_slices_ - 1) & 1], 0), "join chain stream");
     if (cur_slices_ >= 2) cuda_check(cudaStreamWaitEvent(st, ev_dx_[cur_slices_ & 1], 0), "join chain stream");

@@ -100,7 +100,7 @@ class FusedRank {
   void dequant(const int* plan, int j, int b, bool with_g, cudaStream_t st);
   // `c`: the output's tensor map (weight-gradient mode: tiled stores of the bf16 gradient); null otherwise.
   void launch_gemm(int mode, const GemmParams& p, const CUtensorMap& a, const CUtensorMap& b, cudaStream_t st,
-                   const CUtensorMap* c = nullptr);
+                   const CUtensorMap* c = nullptr, int spare_sms = 0);
 
   int P_, L_, me_, S_, D_, F_, K_, stripe_, tk_cap_, max_slices_, num_sms_, put_blocks_;
   // `cta_pairs_`: the row-wise GEMM modes run as CTA pairs (256-row tiles). `tgmm_pairs_`: the weight-gradient mode
@@ -116,6 +116,7 @@ class FusedRank {
   torch::Tensor act_[2], h_[2], dy_[2], dh_[2], dwp_[2];
   torch::Tensor carry_up_, carry_down_, pass_base_, expected_total_, status_, tables_,
       sort_scratch_, my_counts_;
+  torch::Tensor ready_, ready_base_, ready_total_;  // fp8 wire: per-expert "rows expanded" counter, its base, its target
   // device pointer tables, rows of `tables_`
   enum Table { kTabX, kTabG, kTabW, kTabXq, kTabGq, kTabXs, kTabGs, kTabArrive, kTabRet, kTabDw, kTabCount,
                kTabCredit, kTabTraffic0, kTabTraffic1, kTabTflags0, kTabTflags1, kNumTables };
@@ -127,6 +128,8 @@ class FusedRank {
   std::map<std::tuple<const void*, uint32_t, int64_t, int64_t>, CUtensorMap> weight_maps_;
 
   cudaStream_t comm_stream_ = nullptr, aux_stream_ = nullptr, chain_[2] = {};
+  cudaStream_t expand_stream_ = nullptr;  // fp8 wire: the expansion kernels run here, beside the GEMM chains
+  cudaEvent_t ev_expand_[4] = {};  // expansion of slice j (mod 4) has finished
   cudaEvent_t ev_down_[2] = {}, ev_dd_[2] = {}, ev_ds_[2] = {}, ev_dx_[2] = {}, ev_tgd_[2] = {}, ev_tgu_[2] = {};
   cudaEvent_t ev_pass_ = nullptr, ev_put_[4] = {}, ev_done_[4] = {}, ev_header_ = nullptr;
   int64_t last_slices_ = -1;  // slice count of the previous forward pass (the next pass's guess)
