@@ -117,7 +117,8 @@ def main():
     _build.build()
     print("extension: built for sm_100a at", os.path.relpath(_build._so_path()))
     if not args.skip_ptxas:
-        print("\nkernel resources (ptxas -v; dynamic shared memory of the GEMM kernels: 230656 B per CTA)")
+        print(f"\nkernel resources (ptxas -v; dynamic shared memory of the GEMM kernels: "
+              f"{_build.load().gemm_smem_bytes} B per CTA)")
         print(f"{'file':28s} {'kernel':60s} {'regs':>5s} {'spill B':>8s} {'static smem B':>14s}")
         for src, name, regs, spill, smem in ptxas_report():
             print(f"{src:28s} {name[:60]:60s} {regs:5d} {spill:8d} {smem:14d}")

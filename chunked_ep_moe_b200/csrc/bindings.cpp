@@ -87,6 +87,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("arena_zero", &cem::arena_zero);
   m.def("arena_fill", &cem::arena_fill, "cudaMemset of a byte range (tests poison data buffers with NaN patterns)");
   m.def("arena_layout", &arena_layout_dict, "byte offsets inside one rank's symmetric arena");
+  m.def("arena_read_i32", &cem::arena_read_i32, "device synchronise + copy int32 values of an arena to the host");
+  m.attr("gemm_smem_bytes") = cem::kGemmSmemBytes;
   m.def("pair_grid_used", []() { return cem::g_pair_grid_used; }, "grid of the last CTA-pair GEMM launch");
   m.def("wait_probe", &wait_probe, "bounded-wait self test kernel");
   m.def("format_status", &cem::format_status, "text of a recorded status block");

@@ -72,8 +72,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
   }
 }
 
-// Non-suspending variant (test_wait polling) for barriers completed by the other CTA of a pair.
-__device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, uint32_t limit_us) {
+// Non-suspending variant (test_wait polling) for barriers completed by the other CTA of a pair; also gives up as
+// soon as `*abort` is set.
+__device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, uint32_t limit_us,
+                                               const volatile int* abort = nullptr) {
   uint64_t t0 = 0;
   for (uint32_t i = 0;; ++i) {
     uint32_t ok;
@@ -88,6 +90,7 @@ __device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, ui
         : "memory");
     if (ok) return true;
     if ((i & 255u) == 255u) {
+      if (abort != nullptr && *abort != 0) return false;
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
       else if (now - t0 > static_cast<uint64_t>(limit_us) * 1000ull) return false;

@@ -170,37 +170,46 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
     unsigned long long dst = 0;
     if (src >= 0)
       dst = reinterpret_cast<unsigned long long>(p.peer_rows[src] + static_cast<size_t>(pos) * p.ld0 + tl.n * kBlockN);
-    // Every lane stages its own row (two 128-column halves, 256 bytes each) and hands it to the async proxy as one
-    // bulk store to the source rank. Nothing here depends on another lane, and nobody waits for a remote store: the
-    // copy engine keeps the stores of consecutive tiles in flight while the warp goes on to the next accumulator.
-    uint8_t* my_row = stage_gen + lane * kStageRowPitch;
+    // Rows leave through the async proxy: a lane stages its WHOLE row of the tile (256 columns, 512 bytes) and hands it
+    // to the copy engine as one bulk store to the source rank. The warp's staging holds 16 rows, so lanes 0-15 go first
+    // and lanes 16-31 follow once the first sixteen stores have read their rows (TMEM is simply read twice). Nobody
+    // waits for a remote store: the copy engine keeps the stores of consecutive tiles in flight while the warp goes
+    // on to the next accumulator. Row pitch 528 bytes: eight neighbouring lanes hit eight different bank groups.
+    uint8_t* my_row = stage_gen + (lane & 15) * kStageRowPitch;
     const uint32_t my_row_s = smem_u32(my_row);
 #pragma unroll 1
-    for (int half = 0; half < 2; ++half) {
-      bulk_wait_read();  // my previous store has read this staging row
+    for (int pass = 0; pass < 2; ++pass) {
+      const bool mine = (lane >> 4) == pass;
+      // The lane that used this staging row last (this lane or its partner 16 lanes away) has had it read.
+      bulk_wait_read();
+      __syncwarp();
 #pragma unroll 1
-      for (int c = 0; c < 4; c += 2) {
+      for (int c = 0; c < 8; c += 2) {
         uint32_t r2[32];
-        tmem_ld_32x32(tacc + half * 128 + c * 32, r);
-        tmem_ld_32x32(tacc + half * 128 + c * 32 + 32, r2);
+        tmem_ld_32x32(tacc + c * 32, r);
+        tmem_ld_32x32(tacc + c * 32 + 32, r2);
         tmem_ld_wait();
+        if (mine) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          *reinterpret_cast<int4*>(my_row + (c * 4 + i) * 16) =
-              make_int4(pack_bf16(__uint_as_float(r[8 * i]) * w, __uint_as_float(r[8 * i + 1]) * w),
-                        pack_bf16(__uint_as_float(r[8 * i + 2]) * w, __uint_as_float(r[8 * i + 3]) * w),
-                        pack_bf16(__uint_as_float(r[8 * i + 4]) * w, __uint_as_float(r[8 * i + 5]) * w),
-                        pack_bf16(__uint_as_float(r[8 * i + 6]) * w, __uint_as_float(r[8 * i + 7]) * w));
-          *reinterpret_cast<int4*>(my_row + (c * 4 + 4 + i) * 16) =
-              make_int4(pack_bf16(__uint_as_float(r2[8 * i]) * w, __uint_as_float(r2[8 * i + 1]) * w),
-                        pack_bf16(__uint_as_float(r2[8 * i + 2]) * w, __uint_as_float(r2[8 * i + 3]) * w),
-                        pack_bf16(__uint_as_float(r2[8 * i + 4]) * w, __uint_as_float(r2[8 * i + 5]) * w),
-                        pack_bf16(__uint_as_float(r2[8 * i + 6]) * w, __uint_as_float(r2[8 * i + 7]) * w));
+          for (int i = 0; i < 4; ++i) {
+            *reinterpret_cast<int4*>(my_row + (c * 4 + i) * 16) =
+                make_int4(pack_bf16(__uint_as_float(r[8 * i]) * w, __uint_as_float(r[8 * i + 1]) * w),
+                          pack_bf16(__uint_as_float(r[8 * i + 2]) * w, __uint_as_float(r[8 * i + 3]) * w),
+                          pack_bf16(__uint_as_float(r[8 * i + 4]) * w, __uint_as_float(r[8 * i + 5]) * w),
+                          pack_bf16(__uint_as_float(r[8 * i + 6]) * w, __uint_as_float(r[8 * i + 7]) * w));
+            *reinterpret_cast<int4*>(my_row + (c * 4 + 4 + i) * 16) =
+                make_int4(pack_bf16(__uint_as_float(r2[8 * i]) * w, __uint_as_float(r2[8 * i + 1]) * w),
+                          pack_bf16(__uint_as_float(r2[8 * i + 2]) * w, __uint_as_float(r2[8 * i + 3]) * w),
+                          pack_bf16(__uint_as_float(r2[8 * i + 4]) * w, __uint_as_float(r2[8 * i + 5]) * w),
+                          pack_bf16(__uint_as_float(r2[8 * i + 6]) * w, __uint_as_float(r2[8 * i + 7]) * w));
+          }
         }
       }
-      fence_proxy_async_smem();
-      if (dst != 0) bulk_store(dst + half * 256, my_row_s, 256);
-      bulk_commit();
+      if (mine) {
+        fence_proxy_async_smem();
+        if (dst != 0) bulk_store(dst, my_row_s, 512);
+        bulk_commit();
+      }
     }
     if constexpr (MODE == kModeDx) {
       if (tl.n == 0 && src >= 0) {

@@ -86,14 +86,18 @@ struct GemmParams {
 constexpr int kStageBytesA = kBlockM * kBlockK * 2;
 constexpr int kStageBytesB = kBlockN * kBlockK * 2;
 constexpr int kStageBytes = kStageBytesA + kStageBytesB;
-// Epilogue staging, per epilogue warp: 32 rows x (256 bytes = 128 bf16 columns, + 16 bytes of padding so that the
-// 16-byte pieces eight neighbouring lanes write at the same column fall into eight different bank groups).
-constexpr int kStageRowPitch = 272;
-constexpr int kStagingBytes = 4 * 32 * kStageRowPitch;
+// Epilogue staging, per epilogue warp: 16 rows x (512 bytes = the tile's 256 bf16 columns, + 16 bytes of padding so
+// that the 16-byte pieces eight neighbouring lanes write at the same column fall into eight different bank groups);
+// the weight-gradient mode uses the same space as two swizzled 4 KB blocks. The total leaves room for one small CTA
+// of another kernel (a put, an fp8 expansion) beside a persistent GEMM CTA: 228 KB per SM, 1 KB reserved per CTA.
+constexpr int kStageRowPitch = 528;
+constexpr int kStagingBytes = 4 * 16 * kStageRowPitch;
+static_assert(kStagingBytes >= 4 * 8192, "the weight-gradient mode stages two 4 KB blocks per epilogue warp");
 constexpr int kSmemAlignSlack = 512;  // the kernels check at run time that the 1024-byte aligned layout fits
 constexpr int kSmemTailBytes = 256;   // barriers, TMEM slot, flags
 constexpr int kGemmSmemBytes = kSmemAlignSlack + kStages * kStageBytes + kStagingBytes + kSmemTailBytes;
 static_assert(kGemmSmemBytes <= 232448, "more shared memory than one CTA can have");
+static_assert(kGemmSmemBytes + 1024 + 1024 + 16 <= 233472, "no room for a second, small CTA on the SM");
 
 // `map_c`: weight-gradient mode only, the bf16 gradient [L*M, N] with boxes of 32 rows x 64 columns (tiled stores);
 // the other modes ignore it (pass any valid map).

@@ -117,6 +117,14 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
     atomicAdd(p.prof + static_cast<size_t>(blockIdx.x) * kProfSlots + slot, static_cast<unsigned long long>(v));
   };
 
+  // A CTA that gives up tells its partner too (the flag sits at the same offset in both CTAs), so the partner's waits
+  // end at their next poll instead of running into their own limits.
+  const uint32_t partner_abort = map_to_cta(bar_base + kSlotOff + 4, static_cast<uint32_t>(rank ^ 1));
+  auto raise_abort = [&]() {
+    *abort_flag = 1;
+    st_shared_cluster_u32(partner_abort, 1u);
+  };
+
   // The aligned layout must fit into what the launch provided. Both CTAs of a pair see the same offsets, so they
   // leave together.
   if (smem_base - smem_u32(smem_raw) > static_cast<uint32_t>(kSmemAlignSlack)) {
@@ -182,17 +190,20 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
         if (t + tile_step < num_tiles) nxt = decode_pair_tile<MODE>(p, t + tile_step, num_entries, rank);
         if constexpr (MODE == kModeSwiglu) {
           if ((p.arrive != nullptr || p.ready != nullptr) && tl.g != waited_expert) {
-            if (!wait_expert_rows(p, tl.g, lane, abort_flag)) break;
+            if (!wait_expert_rows(p, tl.g, lane, abort_flag)) {
+              if (lane == 0) raise_abort();
+              break;
+            }
             waited_expert = tl.g;
           }
         }
         for (int kb = 0; kb < tl.kblocks; ++kb) {
           const long long w0 = counting ? clock64() : 0;
-          const bool ok = __all_sync(0xffffffffu, mbar_wait_poll(empty_bar(ps), pph ^ 1u, p.mbar_limit));
+          const bool ok = __all_sync(0xffffffffu, mbar_wait_poll(empty_bar(ps), pph ^ 1u, p.mbar_limit, abort_flag));
           if (!ok) {
             if (lane == 0) {
               report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1100 + ps, 0, 0);
-              *abort_flag = 1;
+              raise_abort();
             }
             dead = true;
             break;
@@ -252,7 +263,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
       auto fail = [&](int t, int detail) {
         if (lane == 0) {
           report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, detail, 0, 0);
-          *abort_flag = 1;
+          raise_abort();
         }
         dead = true;
       };
@@ -274,15 +285,15 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
         bool ok = true;
         if (leader) {
           const long long w0 = counting ? clock64() : 0;
-          ok = __all_sync(0xffffffffu, mbar_wait_poll(acc_empty_bar(as), aph ^ 1u, p.mbar_limit));
+          ok = __all_sync(0xffffffffu, mbar_wait_poll(acc_empty_bar(as), aph ^ 1u, p.mbar_limit, abort_flag));
           if (counting) acc_wait += clock64() - w0;
           if (!ok) { fail(t, 1200 + as); break; }
           tcgen05_fence_after_sync();
         }
         for (int kb = 0; kb < solo_kblocks; ++kb) {
           const long long w1 = counting ? clock64() : 0;
-          ok = mbar_wait(full_bar(cs), cph, p.mbar_limit);
-          if (ok && kRelay && leader) ok = mbar_wait_poll(ready_bar(cs), cph, p.mbar_limit);
+          ok = mbar_wait(full_bar(cs), cph, p.mbar_limit, abort_flag);
+          if (ok && kRelay && leader) ok = mbar_wait_poll(ready_bar(cs), cph, p.mbar_limit, abort_flag);
           ok = __all_sync(0xffffffffu, ok);
           if (counting) full_wait += clock64() - w1;
           if (!ok) { fail(t, 1300 + cs); break; }
@@ -298,7 +309,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
         if constexpr (kRelay) {
           if (ragged_tail) {
             const int kb = tl.kblocks - 1;
-            ok = __all_sync(0xffffffffu, mbar_wait(full_bar(cs), cph, p.mbar_limit));
+            ok = __all_sync(0xffffffffu, mbar_wait(full_bar(cs), cph, p.mbar_limit, abort_flag));
             if (!ok) { fail(t, 1300 + cs); break; }
             const int valid = tl.nrows - kb * kBlockK;
             const int ksteps = (valid + kUmmaK - 1) / kUmmaK;
@@ -313,7 +324,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
             if (!leader) {
               if (elect_one()) mbar_arrive_cluster(map_to_cta(ready_bar(cs), peer));
             } else {
-              ok = __all_sync(0xffffffffu, mbar_wait_poll(ready_bar(cs), cph, p.mbar_limit));
+              ok = __all_sync(0xffffffffu, mbar_wait_poll(ready_bar(cs), cph, p.mbar_limit, abort_flag));
               if (!ok) { fail(t, 1400 + cs); break; }
               tcgen05_fence_after_sync();
               issue_stage(cs, tmem_d, ksteps, kb == 0);
@@ -359,10 +370,10 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
       if (t + tile_step < num_tiles) nxt = decode_pair_tile<MODE>(p, t + tile_step, num_entries, rank);
       const int as = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1u;
-      bool ok = mbar_wait_poll(acc_full_bar(as), aph, p.mbar_limit);
+      bool ok = mbar_wait_poll(acc_full_bar(as), aph, p.mbar_limit, abort_flag);
       if (!ok) {
         report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1500 + as, 0, 0);
-        *abort_flag = 1;
+        raise_abort();
       }
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;

@@ -768,6 +768,16 @@ void arena_zero(int64_t ptr, int64_t bytes) {
   cuda_check(cudaDeviceSynchronize(), "arena sync");
 }
 
+torch::Tensor arena_read_i32(int64_t ptr, int64_t offset_bytes, int64_t count) {
+  expect(ptr != 0 && offset_bytes >= 0 && offset_bytes % 4 == 0 && count >= 0, "bad arena range");
+  torch::Tensor out = torch::empty({count}, torch::kInt32);
+  cuda_check(cudaDeviceSynchronize(), "arena sync");
+  cuda_check(cudaMemcpy(out.data_ptr(), reinterpret_cast<const uint8_t*>(ptr) + offset_bytes,
+                        static_cast<size_t>(count) * 4, cudaMemcpyDeviceToHost),
+             "arena read");
+  return out;
+}
+
 void arena_fill(int64_t ptr, int64_t bytes, int value) {
   cuda_check(cudaMemset(reinterpret_cast<void*>(ptr), value, static_cast<size_t>(bytes)), "arena memset");
   cuda_check(cudaDeviceSynchronize(), "arena sync");

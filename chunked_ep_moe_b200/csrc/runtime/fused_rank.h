@@ -152,5 +152,7 @@ int64_t arena_import(py::bytes handle);
 void arena_close(int64_t ptr);
 void arena_zero(int64_t ptr, int64_t bytes);
 void arena_fill(int64_t ptr, int64_t bytes, int value);
+// Synchronises the device and copies `count` int32 values at `ptr + offset_bytes` to a CPU tensor (tests read counters).
+torch::Tensor arena_read_i32(int64_t ptr, int64_t offset_bytes, int64_t count);
 
 }  // namespace cem

@@ -418,3 +418,39 @@ def test_bounded_wait_reports_instead_of_hanging():
     st = status.cpu().tolist()
     assert st[0] == 2 and st[1] == 5 and st[5] == 5 and st[6] == 0, st
     assert float(torch.ones(4, device="cuda").sum()) == 4.0  # the device still answers
+
+
+@pytest.mark.parametrize("skew", ["uniform", "all_one", "rank0"])
+def test_buffers_and_wire_rows_do_not_depend_on_the_routing(skew):
+    """Whatever the routing, a rank holds the same bytes (every per-iteration buffer is S rows) and receives exactly
+    the rows the traffic matrix says, no padding: the arrival counters of every (source, expert) segment end at that
+    segment's row count."""
+    from chunked_ep_moe_b200 import _build
+    from chunked_ep_moe_b200.parallel.lockstep import LockstepWorld
+
+    ext = _build.load()
+    P, E, K, D, F, T, S = 4, 8, 2, 256, 256, 96, 64
+    cfg = ChunkedMoEConfig(num_experts=E, top_k=K, slice_size=S, transport="nvshmem", expert_compute="fused",
+                           stripe_width=64)
+    x, ids, weights, w_up, w_down, _ = moe_cases.setup(P, T, E, K, D, F, skew, seed=2)
+    bf = lambda t: t.cuda().to(torch.bfloat16)
+    sh = lambda t, r: moe_cases.shard(t, r, P)
+    world = LockstepWorld(cfg, P, D, F, T, cta_pairs=False)
+    # geometry alone fixes what a rank holds; the routing is not an argument of either size
+    assert world.arenas.nbytes == ext.arena_bytes(P, E // P, S, D, T * K, False)
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_allocated()
+    outs, saved = world.forward([bf(sh(x, r)) for r in range(P)], [sh(ids, r).cuda() for r in range(P)],
+                                [sh(weights, r).cuda() for r in range(P)], [bf(sh(w_up, r)) for r in range(P)],
+                                [bf(sh(w_down, r)) for r in range(P)])
+    torch.cuda.synchronize()
+    counts = torch.stack([torch.bincount(sh(ids, r).reshape(-1).long(), minlength=E) for r in range(P)])  # [s, e]
+    lay = ext.arena_layout(P, E // P, S, D, T * K, False)
+    L = E // P
+    for r in range(P):
+        arrived = ext.arena_read_i32(world.arenas.bases[r], lay["arrive"], P * L).reshape(P, L)
+        assert torch.equal(arrived.long(), counts[:, r * L:(r + 1) * L]), f"rank {r}: rows received != rows routed"
+    del outs, saved
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() <= before + (1 << 20), "a pass must not grow what the ranks hold"
+    world.close()
