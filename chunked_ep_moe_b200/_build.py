@@ -28,6 +28,8 @@ _SOURCES = [
     "comm/comm_kernels.cu",
     "plan/plan_kernel.cu",
     "plan/expert_sort_noalloc.cu",
+    "model/model_kernels.cu",
+    "model/model_ops.cpp",
 ]
 _lock = threading.Lock()
 _module = None

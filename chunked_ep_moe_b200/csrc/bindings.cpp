@@ -5,6 +5,7 @@
 
 #include "gemm/grouped_gemm.cuh"
 #include "plan/plan_kernel.cuh"
+#include "model/model_ops.h"
 #include "runtime/fused_rank.h"
 #include "runtime/kernel_runner.h"
 
@@ -92,6 +93,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("pair_grid_used", []() { return cem::g_pair_grid_used; }, "grid of the last CTA-pair GEMM launch");
   m.def("wait_probe", &wait_probe, "bounded-wait self test kernel");
   m.def("format_status", &cem::format_status, "text of a recorded status block");
+  m.def("add_rms_norm_fwd", &cem::add_rms_norm_fwd, "s = x + delta, y = RMSNorm(s) * w -> (s, y, rstd)");
+  m.def("add_rms_norm_bwd", &cem::add_rms_norm_bwd, "-> (ds, dweight)");
+  m.def("rope_qkv_fwd", &cem::rope_qkv_fwd, "qkv [B,S,3,H,hd] -> rotated q, k and v as [B,H,S,hd]");
+  m.def("rope_qkv_bwd", &cem::rope_qkv_bwd, "gradients of q, k, v -> gradient of qkv");
+  m.def("cross_entropy_fwd", &cem::cross_entropy_fwd, "bf16 logits -> (loss per row, log-sum-exp per row)");
+  m.def("cross_entropy_bwd", &cem::cross_entropy_bwd, "-> bf16 gradient of the logits");
   py::class_<cem::KernelRunner>(m, "KernelRunner")
       .def(py::init<int, int, int, int, bool>(), py::arg("L"), py::arg("S"), py::arg("stripe"), py::arg("num_sms"),
            py::arg("cta_pairs") = false)

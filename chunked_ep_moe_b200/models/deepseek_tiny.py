@@ -27,6 +27,7 @@ import torch.nn.functional as F
 
 from ..api import chunked_moe
 from ..config import ChunkedMoEConfig
+from .fused_ops import add_rms_norm, cross_entropy, rope_qkv
 
 
 @dataclasses.dataclass
@@ -67,25 +68,16 @@ class RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(dim))
         self.eps = eps
 
-    def forward(self, x):
-        # fp32 statistics, output in x's dtype; one fused kernel on CUDA instead of six elementwise ones
-        return F.rms_norm(x, (x.shape[-1],), self.weight, self.eps)
+    def forward(self, x, delta=None):
+        """Returns `(s, norm(s))` with `s = x + delta` (`s = x` without a delta): the residual add that precedes every
+        norm in the decoder is folded into the norm's kernel (fp32 statistics, outputs in x's dtype)."""
+        return add_rms_norm(x, delta, self.weight, self.eps)
 
 
 def rope_tables(seq_len: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
     inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
     ang = torch.outer(torch.arange(seq_len, device=device, dtype=torch.float32), inv)
     return ang.cos(), ang.sin()
-
-
-def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-    """x: [B, H, S, hd]; rotates pairs (even, odd) of the head dimension, in fp32.
-
-    Written as one complex multiplication ((x1 + i x2)(cos + i sin)): three kernels instead of eight.
-    """
-    xc = torch.view_as_complex(x.float().reshape(*x.shape[:-1], -1, 2))
-    out = torch.view_as_real(xc * torch.complex(cos, sin)).flatten(-2)
-    return out.to(x.dtype)
 
 
 class Attention(nn.Module):
@@ -98,8 +90,9 @@ class Attention(nn.Module):
 
     def forward(self, x, cos, sin):
         b, s, _ = x.shape
-        q, k, v = self.qkv(x).view(b, s, 3, self.n_heads, self.head_dim).permute(2, 0, 3, 1, 4)
-        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+        # q and k are rotated (pairs (even, odd) of the head dimension, fp32 arithmetic) while they are brought from
+        # the projection's [B, S, 3, H, hd] layout into the attention's [B, H, S, hd]: one kernel for the three tensors
+        q, k, v = rope_qkv(self.qkv(x).view(b, s, 3, self.n_heads, self.head_dim), cos, sin)
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         return self.proj(o.transpose(1, 2).reshape(b, s, -1))
 
@@ -192,12 +185,15 @@ class Block(nn.Module):
         self.ffn = DenseSwiGLU(cfg.d_model, cfg.dense_ffn) if dense else MoEBlock(cfg, group)
         self.dense = dense
 
-    def forward(self, x, cos, sin):
-        x = x + self.attn(self.norm1(x), cos, sin)
+    def forward(self, x, delta, cos, sin):
+        """`x` is the residual stream BEFORE `delta` (the previous block's FFN output, None for the first block) has
+        been added; returns the stream before this block's own FFN output is added, that output, and the aux loss."""
+        x, normed = self.norm1(x, delta)
+        x, normed = self.norm2(x, self.attn(normed, cos, sin))
         if self.dense:
-            return x + self.ffn(self.norm2(x)), x.new_zeros((), dtype=torch.float32)
-        y, aux = self.ffn(self.norm2(x))
-        return x + y, aux
+            return x, self.ffn(normed), x.new_zeros((), dtype=torch.float32)
+        y, aux = self.ffn(normed)
+        return x, y, aux
 
 
 class DeepSeekTiny(nn.Module):
@@ -246,13 +242,13 @@ class DeepSeekTiny(nn.Module):
         if self._rope is None or self._rope[0].shape[0] < s or self._rope[0].device != tokens.device:
             self._rope = rope_tables(s, self.cfg.head_dim, self.cfg.rope_theta, tokens.device)
         cos, sin = self._rope[0][:s], self._rope[1][:s]
-        x = self.embed(tokens)
+        x, delta = self.embed(tokens), None
         aux_total = x.new_zeros((), dtype=torch.float32)
         for blk in self.blocks:
-            x, aux = blk(x, cos, sin)
+            x, delta, aux = blk(x, delta, cos, sin)
             aux_total = aux_total + aux
-        logits = self.lm_head(self.norm(x))
+        _, normed = self.norm(x, delta)
+        logits = self.lm_head(normed)
         if targets is None:
             return logits, aux_total
-        ce = F.cross_entropy(logits.float().reshape(-1, logits.shape[-1]), targets.reshape(-1))
-        return ce, aux_total
+        return cross_entropy(logits.reshape(-1, logits.shape[-1]), targets.reshape(-1)), aux_total
