@@ -52,6 +52,8 @@ def parse_args():
     ap.add_argument("--no-baseline", action="store_true",
                     help="skip timing the NCCL + library grouped-GEMM layer on the same tensors (fills vs_baseline)")
     ap.add_argument("--baseline-steps", type=int, default=2)
+    ap.add_argument("--per-step", action="store_true",
+                    help="also print every timed step's device time on rank 0 (stderr), from events between the steps")
     return ap.parse_args()
 
 
@@ -92,28 +94,91 @@ def bind_near_gpu(index: int) -> str:
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs (read-only queries)."""
+    """Samples SM clock, power and throttle reasons of one GPU while the timed loops run (read-only NVML queries).
+
+    A thread of this process asks NVML every 50 ms (two cheap queries); only rank 0 samples. (One `nvidia-smi -lms` process per rank,
+    started right before the timed loop, cost the first timed step ~9 ms on 4 GPUs while the tools attached to every
+    GPU of the box, and an occasional step later.) Without NVML in the process the `nvidia-smi` loop is the fallback,
+    started before the warm-up so that its start-up is over when the timing begins.
+    """
 
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
-        self.path = tempfile.NamedTemporaryFile(prefix="clocks_", suffix=".csv", delete=False).name
+        self.samples = []  # (monotonic time, sm MHz, reasons bitmask)
+        self.smax = None
+        self.thread = None
         self.proc = None
+        self.path = None
+        self.window = [None, None]
+
+    def _nvml_loop(self, nvml, handle):
+        import threading  # noqa: F401
+
+        while not self._stop:
+            try:
+                mhz = nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM)
+                try:
+                    mask = nvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                except AttributeError:
+                    mask = nvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                self.samples.append((time.monotonic(), float(mhz), int(mask)))
+            except Exception:  # noqa: BLE001 - a failed query is a missing sample
+                pass
+            time.sleep(0.05)
 
     def start(self):
         try:
+            import threading
+
+            import pynvml
+
+            import torch
+
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByUUID("GPU-" + str(torch.cuda.get_device_properties(self.gpu_index).uuid))
+            self.smax = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            self._stop = False
+            self.thread = threading.Thread(target=self._nvml_loop, args=(pynvml, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:  # noqa: BLE001 - fall back to the command-line tool
+            self.thread = None
+        try:
+            self.path = tempfile.NamedTemporaryFile(prefix="clocks_", suffix=".csv", delete=False).name
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
                  "-i", str(self.gpu_index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
+    def mark_begin(self):
+        self.window[0] = time.monotonic()
+
+    def mark_end(self):
+        self.window[1] = time.monotonic()
+
     def stop(self) -> dict:
+        if self.thread is not None:
+            time.sleep(0.25)
+            self._stop = True
+            self.thread.join(timeout=2)
+            lo, hi = self.window[0] or 0.0, self.window[1] or float("inf")
+            inside = [(mhz, mask) for t, mhz, mask in self.samples if lo <= t <= hi] or \
+                     [(mhz, mask) for _, mhz, mask in self.samples]
+            sm = sorted(m for m, _ in inside)
+            seen = 0
+            for _, mask in inside:
+                seen |= mask
+            return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.smax,
+                    "reasons": sorted(name for bit, name in self.REASONS.items() if seen & bit),
+                    "samples": len(sm), "source": "nvml, sampled during the timed loops"}
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no NVML and no nvidia-smi"]}
         time.sleep(0.25)
         self.proc.terminate()
         try:
@@ -138,14 +203,15 @@ class ClockSampler:
         os.unlink(self.path)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "source": "nvidia-smi -lms 200 (whole run)"}
 
 
 class NvlinkCounter:
     """NVLink payload bytes this GPU sent and received, from NVML's per-device throughput counters (read-only).
 
     Used to set the bytes the fused kernels really put on the wire against the algorithmic bytes of the layer. Any
-    failure (no NVML, counters not exposed) yields None: the number is evidence, never a dependency.
+    failure (no NVML, counters not exposed: on this pool's B200 boxes the query answers "not supported") yields None:
+    the number is evidence, never a dependency.
     """
 
     TX, RX = 138, 139  # NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_TX / _RX, KiB since the driver was loaded
@@ -161,6 +227,8 @@ class NvlinkCounter:
             self.nvml = pynvml
             self.handle = pynvml.nvmlDeviceGetHandleByUUID("GPU-" + str(torch.cuda.get_device_properties(index).uuid))
         except Exception:  # noqa: BLE001
+            self.handle = None
+        if self.read() is None:  # counters not exposed on this system: later reads cost nothing
             self.handle = None
 
     def read(self):
@@ -305,6 +373,10 @@ def main():
 
         return fused_mod.launches()
 
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()  # well before the timed region: whatever its start-up costs is over by then
+    nvlink = NvlinkCounter(local_rank)
     for _ in range(max(args.warmup, 3)):
         step(x_d.clone(), ids_d, weights_d.clone())
     sync_all()
@@ -322,18 +394,30 @@ def main():
         del out_c, dx_c, dwt_c
         sync_all()
 
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    nvlink = NvlinkCounter(local_rank)
+    # The check above keeps the GPU idle for seconds and its clocks fall; the first step after an idle spell measured
+    # 9-12 ms longer than the following ones on 4 GPUs. Two more untimed steps bring the device back to the state the
+    # warm-up left it in; only the barrier and the synchronisation sit between them and the timed loop.
+    for _ in range(2):
+        step(x_d.clone(), ids_d, weights_d.clone())
     l0 = launches()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync_all()
+    if sampler:
+        sampler.mark_begin()
     link0 = nvlink.read()
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)] if args.per_step else None
     start.record()
-    for _ in range(args.steps):
+    for i in range(args.steps):
+        if marks:
+            marks[i].record()
         step(x_d.detach(), ids_d, weights_d.detach())
     stop.record()
+    if marks:
+        marks[-1].record()
     sync_all()
+    if marks and rank == 0:
+        print("per-step ms (device-timed loop):",
+              " ".join(f"{marks[i].elapsed_time(marks[i + 1]):.2f}" for i in range(args.steps)), file=sys.stderr)
     link1 = nvlink.read()
     ms = start.elapsed_time(stop) / args.steps
     total_launches = launches() - l0
@@ -350,7 +434,9 @@ def main():
         e1.record()
         sync_all()
         e2e_ms = e0.elapsed_time(e1) / args.steps
-    clocks = sampler.stop()
+    if sampler:
+        sampler.mark_end()
+    clocks = sampler.stop() if sampler else None
 
     # Exposed all-to-all: the same per-GPU work (same L experts, same rows per expert in expectation) with every
     # row local, i.e. this rank alone as a 1-rank expert-parallel group, timed the same way.

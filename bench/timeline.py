@@ -34,6 +34,9 @@ def main():
     ap.add_argument("--slice-size", type=int, default=8192)
     ap.add_argument("--comm-dtype", default=None)
     ap.add_argument("--quiet", action="store_true", help="only the per-kernel summary")
+    ap.add_argument("--steps", type=int, default=1,
+                    help="steps recorded back to back without a host synchronisation between them (per-kernel means "
+                         "then include how kernels of consecutive steps wait for other ranks)")
     args = ap.parse_args()
     import torch.distributed as dist
 
@@ -75,7 +78,8 @@ def main():
         dist.barrier()
         torch.cuda.synchronize()
     with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
-        step()
+        for _ in range(args.steps):
+            step()
         torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
@@ -104,7 +108,9 @@ def main():
     for key, (n, total) in summary.items():
         print(f"{key:32s} {n:6d} {total:10.3f} {total / n:10.3f}")
     flops = 24.0 * D * F * T * K
-    print(f"\nstep span {span:.3f} ms   {T / (span / 1e3):.0f} tokens/s   {flops / (span / 1e3) / 1e12:.0f} TFLOP/s")
+    span /= args.steps
+    print(f"\nstep span {span:.3f} ms   {T / (span / 1e3):.0f} tokens/s   {flops / (span / 1e3) / 1e12:.0f} TFLOP/s"
+          + (f"   (mean of {args.steps} steps back to back)" if args.steps > 1 else ""))
     if world > 1:
         from chunked_ep_moe_b200.ops import fused
 

@@ -357,16 +357,19 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
 
 }  // namespace
 
+int g_gemm_extra_smem = 0;
+
 void launch_grouped_gemm(int mode, const GemmParams& p, const CUtensorMap& map_a, const CUtensorMap& map_b,
                          const CUtensorMap& map_c, int grid, cudaStream_t stream) {
 #define CEM_LAUNCH(M)                                                                                         \
   case M: {                                                                                                   \
     static bool configured = false;                                                                           \
     if (!configured) {                                                                                        \
-      cudaFuncSetAttribute(grouped_gemm_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes); \
+      cudaFuncSetAttribute(grouped_gemm_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes + 1024); \
       configured = true;                                                                                      \
     }                                                                                                         \
-    grouped_gemm_kernel<M><<<grid, 64 + 32 * epilogue_warps<M>(), kGemmSmemBytes, stream>>>(p, map_a, map_b, map_c);   \
+    grouped_gemm_kernel<M><<<grid, 64 + 32 * epilogue_warps<M>(), kGemmSmemBytes + g_gemm_extra_smem, stream>>>(    \
+        p, map_a, map_b, map_c);                                                                              \
     break;                                                                                                    \
   }
   switch (mode) {

@@ -99,6 +99,11 @@ constexpr int kGemmSmemBytes = kSmemAlignSlack + kStages * kStageBytes + kStagin
 static_assert(kGemmSmemBytes <= 232448, "more shared memory than one CTA can have");
 static_assert(kGemmSmemBytes + 1024 + 1024 + 16 <= 233472, "no room for a second, small CTA on the SM");
 
+// Extra dynamic shared memory (bytes) every GEMM launch asks for beyond what it uses. 0 leaves room for one small CTA
+// of another kernel beside a persistent GEMM CTA; 1024 takes the SM's shared memory for the GEMM CTA alone (put and
+// expansion kernels then only run on SMs a GEMM CTA has left). A measurement knob (`CEM_GEMM_EXCLUSIVE_SM=1`).
+extern int g_gemm_extra_smem;
+
 // `map_c`: weight-gradient mode only, the bf16 gradient [L*M, N] with boxes of 32 rows x 64 columns (tiled stores);
 // the other modes ignore it (pass any valid map).
 void launch_grouped_gemm(int mode, const GemmParams& p, const CUtensorMap& map_a, const CUtensorMap& map_b,

@@ -406,7 +406,7 @@ int resident_pair_grid(Kernel kernel, int requested) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(requested), 1, 1);
   cfg.blockDim = dim3(kGemmThreads, 1, 1);
-  cfg.dynamicSmemBytes = kGemmSmemBytes;
+  cfg.dynamicSmemBytes = kGemmSmemBytes + g_gemm_extra_smem;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
@@ -435,12 +435,13 @@ void launch_grouped_gemm_pair(int mode, const GemmParams& p, const CUtensorMap& 
     static int resident = 0;                                                                                     \
     if (resident == 0) {                                                                                         \
       cudaFuncSetAttribute(grouped_gemm_pair_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
-                           kGemmSmemBytes);                                                                      \
+                           kGemmSmemBytes + 1024);                                                               \
       resident = resident_pair_grid(grouped_gemm_pair_kernel<M>, grid);                                          \
     }                                                                                                            \
     const int g = grid < resident ? grid : resident;                                                             \
     g_pair_grid_used = g;                                                                                        \
-    grouped_gemm_pair_kernel<M><<<g, kGemmThreads, kGemmSmemBytes, stream>>>(p, map_a, map_b, map_c);                   \
+    grouped_gemm_pair_kernel<M><<<g, kGemmThreads, kGemmSmemBytes + g_gemm_extra_smem, stream>>>(p, map_a, map_b,      \
+                                                                                                  map_c);        \
     break;                                                                                                       \
   }
   switch (mode) {

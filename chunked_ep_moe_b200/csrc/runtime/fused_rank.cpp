@@ -92,6 +92,7 @@ FusedRank::FusedRank(int P, int L, int me, int S, int D, int F, int K, int strip
   expect(S % 8 == 0 && S >= 8, "fused kernels need slice_size % 8 == 0");
   expect(!fp8 || D % 128 == 0, "fp8 wire needs D % 128 == 0");
   spin_limit_ = static_cast<uint32_t>(spin_limit);
+  if (const char* v = std::getenv("CEM_GEMM_EXCLUSIVE_SM")) g_gemm_extra_smem = std::atoi(v) != 0 ? 1024 : 0;
   mbar_limit_ = 20u * 1000u * 1000u;  // microseconds: longer than any legitimate wait on another rank
   lay_ = make_plan_layout(P, L, S, max_slices);
   arena_lay_ = make_arena_layout(P, L, S, D, tk_cap, fp8);
@@ -164,6 +165,9 @@ FusedRank::FusedRank(int P, int L, int me, int S, int D, int F, int K, int strip
     // The put and expansion kernels feed kernels that wait for them: their blocks go first when SMs free up.
     int prio_low = 0, prio_high = 0;
     cuda_check(cudaDeviceGetStreamPriorityRange(&prio_low, &prio_high), "stream priority range");
+    if (const char* v = std::getenv("CEM_COMM_PRIORITY")) {
+      if (std::atoi(v) == 0) prio_high = prio_low;  // measurement knob: comm streams at the default priority
+    }
     cuda_check(cudaStreamCreateWithPriority(&comm_stream_, cudaStreamNonBlocking, prio_high), "comm stream");
     cuda_check(cudaStreamCreateWithFlags(&aux_stream_, cudaStreamNonBlocking), "aux stream");
     for (int q = 0; q < 2; ++q) cuda_check(cudaStreamCreateWithFlags(&chain_[q], cudaStreamNonBlocking), "chain stream");

@@ -55,11 +55,12 @@ def striped_swiglu(h: torch.Tensor, stripe: int) -> torch.Tensor:
 
 
 def striped_swiglu_bwd(h: torch.Tensor, d_act: torch.Tensor, stripe: int) -> torch.Tensor:
-    """Gradient of `striped_swiglu` w.r.t. its striped input `h` (same striping as `h`)."""
+    """Gradient of `striped_swiglu` w.r.t. its striped input `h` (same striping as `h`), evaluated in fp32.
+
+    With s = sigmoid(gate): d(silu)/d(gate) = s * (1 + gate * (1 - s)), so
+    `d_gate = d_act * up * s * (1 + gate * (1 - s))` and `d_up = d_act * gate * s`.
+    """
     gate, up = split_stripes(h.float(), stripe)
-    d_act = d_act.float()
-    sig = torch.sigmoid(gate)
-    silu = gate * sig
-    d_gate = d_act * up * (sig + silu * (1.0 - sig))
-    d_up = d_act * silu
-    return join_stripes(d_gate, d_up, stripe).to(h.dtype)
+    s = torch.sigmoid(gate)
+    scaled = d_act.float() * s
+    return join_stripes(scaled * up * (1.0 + gate * (1.0 - s)), scaled * gate, stripe).to(h.dtype)

@@ -40,6 +40,7 @@ def test_clock_sample_parser(tmp_path):
     sampler = bench.ClockSampler(0)
     sampler.proc = type("P", (), {"terminate": lambda s: None, "wait": lambda s, timeout=None: 0,
                                    "kill": lambda s: None})()
+    sampler.path = str(tmp_path / "clocks.csv")
     with open(sampler.path, "w") as f:
         f.write("0, 1320, 1965, 998.1, 0x0000000000000004, Not Active, Not Active, Not Active, Active\n")
         f.write("0, 1340, 1965, 1001.7, 0x0000000000000004, Not Active, Not Active, Not Active, Active\n")
@@ -48,6 +49,20 @@ def test_clock_sample_parser(tmp_path):
     got = sampler.stop()
     assert got["sm_mhz"] == 1340.0 and got["sm_max_mhz"] == 1965.0
     assert got["reasons"] == ["sw_power_cap"] and got["samples"] == 3
+
+
+def test_clock_samples_from_nvml_are_cut_to_the_timed_window():
+    """The in-process sampler: only samples between the two marks count; reasons are decoded from NVML's bit mask."""
+    sampler = bench.ClockSampler(0)
+    sampler.thread = type("T", (), {"join": lambda s, timeout=None: None})()
+    sampler._stop = False
+    sampler.smax = 1965.0
+    sampler.samples = [(1.0, 1965.0, 0x0), (2.0, 1300.0, 0x4), (2.2, 1320.0, 0x4), (2.4, 1310.0, 0x4 | 0x20),
+                       (9.0, 1965.0, 0x0)]
+    sampler.window = [1.5, 3.0]
+    got = sampler.stop()
+    assert got["sm_mhz"] == 1310.0 and got["sm_max_mhz"] == 1965.0 and got["samples"] == 3
+    assert got["reasons"] == ["sw_power_cap", "sw_thermal_slowdown"]
 
 
 def test_compile_report_pieces():
