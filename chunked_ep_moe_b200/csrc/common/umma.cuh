@@ -408,6 +408,11 @@ __device__ __forceinline__ bool spin_until_reached(const uint32_t* p, uint32_t t
   return true;
 }
 
+// Asks L2 for the line that holds `p` (no register, no wait).
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
 __device__ __forceinline__ int4 ld_nc_v4(const void* p) {
   int4 v;
   asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0, %1, %2, %3}, [%4];"

@@ -105,6 +105,27 @@ __device__ __forceinline__ bool wait_expert_rows(const GemmParams& p, int g, int
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
 
+// Called by an epilogue warp BEFORE it waits for the tile's accumulator: asks L2 for the row-wise inputs the epilogue
+// will read (the output gradient's columns for the down -> d_weight mode, the gate/up pre-activations for the
+// SwiGLU' mode), so that the mainloop's duration hides their DRAM latency. Lane = tile row, as in the epilogue.
+template <int MODE>
+__device__ __forceinline__ void prefetch_epilogue_inputs(const GemmParams& p, const Tile& tl, int q, int lane) {
+  if constexpr (MODE == kModeDownDw || MODE == kModeDswiglu) {
+    const int row = q * 32 + lane;
+    if (row >= tl.nrows) return;
+    const size_t grow = static_cast<size_t>(tl.row0 + row);
+    if constexpr (MODE == kModeDownDw) {
+      const __nv_bfloat16* g_row = p.in0 + grow * p.ld0 + tl.n * kBlockN;  // 256 columns = four 128-byte lines
+#pragma unroll
+      for (int i = 0; i < 4; ++i) prefetch_l2(g_row + 64 * i);
+    } else {
+      const __nv_bfloat16* h_row = p.in0 + grow * p.ld0 + 2 * tl.n * kBlockN;  // the tile's 512 striped columns
+#pragma unroll
+      for (int i = 0; i < 8; ++i) prefetch_l2(h_row + 64 * i);
+    }
+  }
+}
+
 // `col0`, `ncols` (weight-gradient mode only): the accumulator columns this warp is responsible for; that mode may
 // run two epilogue warps per TMEM lane quarter, each taking half of the columns.
 // Epilogue of one 128 x 256 accumulator tile. `tacc` is this warp's TMEM address (lane quarter q, accumulator
@@ -270,18 +291,44 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
   } else if constexpr (MODE == kModeDswiglu) {
     const __nv_bfloat16* h_row = p.in0 + static_cast<size_t>(grow) * p.ld0;
     __nv_bfloat16* dh_row = p.out0 + static_cast<size_t>(grow) * p.ld0;
+    auto gate_col = [&](int c) {  // striped column of the gate values that belong to accumulator chunk c
+      const int f = tl.n * kBlockN + c * 32;
+      const int b = f / p.stripe;
+      return 2 * b * p.stripe + (f - b * p.stripe);
+    };
+    // The gate/up values of the NEXT 32 columns are requested before this chunk's accumulator is waited for, so their
+    // global-load latency hides behind the TMEM load and the arithmetic (with 16-32 k-blocks per tile this epilogue,
+    // not the mainloop, set the pace).
+    int4 hg_next[4] = {}, hu_next[4] = {};
+    if (valid) {
+      const int g0 = gate_col(0);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        hg_next[i] = *reinterpret_cast<const int4*>(h_row + g0 + 8 * i);
+        hu_next[i] = *reinterpret_cast<const int4*>(h_row + g0 + p.stripe + 8 * i);
+      }
+    }
 #pragma unroll 1
     for (int c = 0; c < 8; ++c) {
-      const int f = tl.n * kBlockN + c * 32;
-      const int b = f / p.stripe, off = f - b * p.stripe;
-      const int gcol = 2 * b * p.stripe + off, ucol = gcol + p.stripe;
+      const int gcol = gate_col(c), ucol = gcol + p.stripe;
+      int4 hg_cur[4], hu_cur[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { hg_cur[i] = hg_next[i]; hu_cur[i] = hu_next[i]; }
       tmem_ld_32x32(tacc + c * 32, r);
+      if (valid && c + 1 < 8) {
+        const int gn = gate_col(c + 1);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          hg_next[i] = *reinterpret_cast<const int4*>(h_row + gn + 8 * i);
+          hu_next[i] = *reinterpret_cast<const int4*>(h_row + gn + p.stripe + 8 * i);
+        }
+      }
       tmem_ld_wait();
       if (valid) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int4 hg = *reinterpret_cast<const int4*>(h_row + gcol + 8 * i);
-          const int4 hu = *reinterpret_cast<const int4*>(h_row + ucol + 8 * i);
+          const int4 hg = hg_cur[i];
+          const int4 hu = hu_cur[i];
           const uint32_t gw[4] = {static_cast<uint32_t>(hg.x), static_cast<uint32_t>(hg.y),
                                   static_cast<uint32_t>(hg.z), static_cast<uint32_t>(hg.w)};
           const uint32_t uw[4] = {static_cast<uint32_t>(hu.x), static_cast<uint32_t>(hu.y),

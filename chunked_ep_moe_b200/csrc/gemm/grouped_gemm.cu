@@ -322,6 +322,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant_
     for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x, ++tcount) {
       const Tile tl = nxt;
       if (t + static_cast<int>(gridDim.x) < num_tiles) nxt = decode_tile<MODE>(p, t + static_cast<int>(gridDim.x), num_entries);
+      prefetch_epilogue_inputs<MODE>(p, tl, warp & 3, lane);
       const int as = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1u;
       const long long w0 = counting ? clock64() : 0;

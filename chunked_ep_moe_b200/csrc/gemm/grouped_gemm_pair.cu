@@ -368,6 +368,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
     for (int t = first_tile; t < num_tiles && !*abort_flag; t += tile_step, ++tcount) {
       const Tile tl = nxt;
       if (t + tile_step < num_tiles) nxt = decode_pair_tile<MODE>(p, t + tile_step, num_entries, rank);
+      prefetch_epilogue_inputs<MODE>(p, tl, warp & 3, lane);
       const int as = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1u;
       bool ok = mbar_wait_poll(acc_full_bar(as), aph, p.mbar_limit, abort_flag);
