@@ -105,6 +105,77 @@ __device__ __forceinline__ bool wait_expert_rows(const GemmParams& p, int g, int
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
 
+// ---------------------------------------------------------------------------------------------
+// Row blocks through the warp's staging buffer: 32 rows x 256 bytes, 16-byte pieces XOR-swizzled by row.
+// The epilogues compute with one tile row per thread, but a warp access that touches 32 different rows costs the
+// SM 32 requests towards L2, as many as 32 full lines; at 16-32 k-blocks per tile that request traffic, not the tensor
+// pipe, set the pace. So row-wise inputs and outputs cross shared memory: threads read and write their own row in the
+// staging block, and the warp moves the block to and from global memory 16 lanes per row (two full 256-byte row
+// pieces per instruction, 8x fewer requests).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void stage_put(uint8_t* stage, int lane, int piece, int4 v) {
+  *reinterpret_cast<int4*>(stage + lane * 256 + ((piece ^ (lane & 15)) << 4)) = v;
+}
+
+__device__ __forceinline__ int4 stage_get(const uint8_t* stage, int lane, int piece) {
+  return *reinterpret_cast<const int4*>(stage + lane * 256 + ((piece ^ (lane & 15)) << 4));
+}
+
+// Staging block -> global: block row r goes to `gbase + r * ld_bytes` (256 bytes); rows >= nvalid are not stored.
+// Shared-memory reads and global stores are issued as two batches: interleaved, every store would have to wait for the
+// read before it and every read for the store before it (the compiler cannot tell that the two do not alias).
+__device__ __forceinline__ void stage_flush(const uint8_t* stage, int lane, uint8_t* gbase, size_t ld_bytes,
+                                            int nvalid) {
+  __syncwarp();
+  const int c16 = lane & 15, rhalf = lane >> 4;
+#pragma unroll
+  for (int batch = 0; batch < 2; ++batch) {
+    int4 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rsel = (batch * 8 + i) * 2 + rhalf;
+      v[i] = *reinterpret_cast<const int4*>(stage + rsel * 256 + ((c16 ^ (rsel & 15)) << 4));
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rsel = (batch * 8 + i) * 2 + rhalf;
+      if (rsel < nvalid) *reinterpret_cast<int4*>(gbase + rsel * ld_bytes + c16 * 16) = v[i];
+    }
+  }
+  __syncwarp();
+}
+
+// Global -> staging block in two steps, so that a caller can put work between the request and the use:
+// `stage_fetch` issues all sixteen 16-byte loads of this lane at once (rows >= nvalid are not read and come out as zeros), `stage_commit` writes them to the staging block.
+__device__ __forceinline__ void stage_fetch(int4 (&v)[16], int lane, const uint8_t* gbase, size_t ld_bytes,
+                                            int nvalid) {
+  const uint8_t* src = gbase + (lane >> 4) * ld_bytes + (lane & 15) * 16;
+  const int mine = nvalid - (lane >> 4);  // this lane loads block rows rhalf, rhalf + 2, ...: those below nvalid
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    v[i] = make_int4(0, 0, 0, 0);
+    if (2 * i < mine) v[i] = *reinterpret_cast<const int4*>(src + static_cast<size_t>(2 * i) * ld_bytes);
+  }
+}
+
+__device__ __forceinline__ void stage_commit(uint8_t* stage, int lane, const int4 (&v)[16]) {
+  __syncwarp();
+  const int c16 = lane & 15, rhalf = lane >> 4;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int rsel = i * 2 + rhalf;
+    *reinterpret_cast<int4*>(stage + rsel * 256 + ((c16 ^ (rsel & 15)) << 4)) = v[i];
+  }
+  __syncwarp();
+}
+
+__device__ __forceinline__ int4 pack8(const uint32_t* r8) {  // eight fp32 accumulator values -> eight bf16
+  return make_int4(pack_bf16(__uint_as_float(r8[0]), __uint_as_float(r8[1])),
+                   pack_bf16(__uint_as_float(r8[2]), __uint_as_float(r8[3])),
+                   pack_bf16(__uint_as_float(r8[4]), __uint_as_float(r8[5])),
+                   pack_bf16(__uint_as_float(r8[6]), __uint_as_float(r8[7])));
+}
+
 // Called by an epilogue warp BEFORE it waits for the tile's accumulator: asks L2 for the row-wise inputs the epilogue
 // will read (the output gradient's columns for the down -> d_weight mode, the gate/up pre-activations for the
 // SwiGLU' mode), so that the mainloop's duration hides their DRAM latency. Lane = tile row, as in the epilogue.
@@ -144,8 +215,9 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
 
   if constexpr (MODE == kModeSwiglu) {
     uint32_t u[32];
-    __nv_bfloat16* act_row = p.out0 + static_cast<size_t>(grow) * p.ld0 + tl.n * (kBlockN / 2);
-    __nv_bfloat16* h_row = p.out1 ? p.out1 + static_cast<size_t>(grow) * p.ld1 + tl.n * kBlockN : nullptr;
+    const int nvalid = plan_clip(tl.nrows - q * 32, 0, 32);  // rows of this warp's 32 that belong to the tile
+    const size_t block_row = static_cast<size_t>(tl.row0 + q * 32);
+    // act: 128 columns = one 256-byte staging block
 #pragma unroll 1
     for (int c = 0; c < 4; ++c) {
       const int f_local = c * 32;
@@ -154,32 +226,38 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
       tmem_ld_32x32(tacc + gcol, r);
       tmem_ld_32x32(tacc + ucol, u);
       tmem_ld_wait();
-      if (valid) {
-        uint32_t o[16];
+      uint32_t o[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float g0 = __uint_as_float(r[2 * i]), g1 = __uint_as_float(r[2 * i + 1]);
-          const float u0 = __uint_as_float(u[2 * i]), u1 = __uint_as_float(u[2 * i + 1]);
-          o[i] = pack_bf16(silu_f(g0) * u0, silu_f(g1) * u1);
-        }
+      for (int i = 0; i < 16; ++i) {
+        const float g0 = __uint_as_float(r[2 * i]), g1 = __uint_as_float(r[2 * i + 1]);
+        const float u0 = __uint_as_float(u[2 * i]), u1 = __uint_as_float(u[2 * i + 1]);
+        o[i] = pack_bf16(silu_f(g0) * u0, silu_f(g1) * u1);
+      }
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-          *reinterpret_cast<int4*>(act_row + f_local + 8 * i) = make_int4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
-        if (h_row != nullptr) {
+      for (int i = 0; i < 4; ++i)
+        stage_put(stage_gen, lane, c * 4 + i, make_int4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]));
+    }
+    stage_flush(stage_gen, lane,
+                reinterpret_cast<uint8_t*>(p.out0 + block_row * p.ld0 + tl.n * (kBlockN / 2)),
+                static_cast<size_t>(p.ld0) * 2, nvalid);
+    if (p.out1 != nullptr) {
+      // h (backward remat): the accumulator's 256 columns ARE the tile's striped pre-activations; two 128-column blocks
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+#pragma unroll 1
+        for (int c = 0; c < 4; c += 2) {
+          tmem_ld_32x32(tacc + half * 128 + c * 32, r);
+          tmem_ld_32x32(tacc + half * 128 + c * 32 + 32, u);
+          tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            *reinterpret_cast<int4*>(h_row + gcol + 8 * i) =
-                make_int4(pack_bf16(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])),
-                          pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
-                          pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])),
-                          pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7])));
-            *reinterpret_cast<int4*>(h_row + ucol + 8 * i) =
-                make_int4(pack_bf16(__uint_as_float(u[8 * i]), __uint_as_float(u[8 * i + 1])),
-                          pack_bf16(__uint_as_float(u[8 * i + 2]), __uint_as_float(u[8 * i + 3])),
-                          pack_bf16(__uint_as_float(u[8 * i + 4]), __uint_as_float(u[8 * i + 5])),
-                          pack_bf16(__uint_as_float(u[8 * i + 6]), __uint_as_float(u[8 * i + 7])));
+            stage_put(stage_gen, lane, c * 4 + i, pack8(r + 8 * i));
+            stage_put(stage_gen, lane, c * 4 + 4 + i, pack8(u + 8 * i));
           }
         }
+        stage_flush(stage_gen, lane,
+                    reinterpret_cast<uint8_t*>(p.out1 + block_row * p.ld1 + tl.n * kBlockN + half * 128),
+                    static_cast<size_t>(p.ld1) * 2, nvalid);
       }
     }
   } else if constexpr (Traits::kCombine) {
@@ -247,48 +325,108 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
     }
   } else if constexpr (MODE == kModeDownDw) {
     const float w = valid ? p.row_w[grow] : 0.0f;
-    const __nv_bfloat16* g_row = p.in0 + static_cast<size_t>(grow) * p.ld0 + tl.n * kBlockN;
-    __nv_bfloat16* dy_row = p.out0 + static_cast<size_t>(grow) * p.ld0 + tl.n * kBlockN;
+    const int nvalid = plan_clip(tl.nrows - q * 32, 0, 32);
+    const size_t block_off = static_cast<size_t>(tl.row0 + q * 32) * p.ld0 + tl.n * kBlockN;
     float partial = 0.0f;
-    // The g chunk of the NEXT 32 columns is requested before this chunk's accumulator is waited for, so its global
-    // load latency hides behind the TMEM load and the arithmetic (this epilogue was the mode's bottleneck).
-    int4 gnext[4] = {};
-    if (valid) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) gnext[i] = *reinterpret_cast<const int4*>(g_row + 8 * i);
-    }
+    // Two 128-column halves: the warp brings its rows' g values into the staging block, every thread turns its own row
+    // into dy = w * g in place (and adds its <g, y> share), the warp writes the block out as dy. The second half's g
+    // values are requested before the first half is worked on.
+    const uint8_t* g_block = reinterpret_cast<const uint8_t*>(p.in0 + block_off);
+    int4 fetched[16];
+    stage_fetch(fetched, lane, g_block, static_cast<size_t>(p.ld0) * 2, nvalid);
 #pragma unroll 1
-    for (int c = 0; c < 8; ++c) {
-      int4 gcur[4];
+    for (int half = 0; half < 2; ++half) {
+      stage_commit(stage_gen, lane, fetched);
+      if (half == 0) stage_fetch(fetched, lane, g_block + 256, static_cast<size_t>(p.ld0) * 2, nvalid);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld_32x32(tacc + half * 128 + c * 32, r);
+        tmem_ld_wait();
+        if (valid) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) gcur[i] = gnext[i];
-      tmem_ld_32x32(tacc + c * 32, r);
-      if (valid && c + 1 < 8) {
+          for (int i = 0; i < 4; ++i) {
+            const int4 gv = stage_get(stage_gen, lane, c * 4 + i);
+            const uint32_t gw[4] = {static_cast<uint32_t>(gv.x), static_cast<uint32_t>(gv.y),
+                                    static_cast<uint32_t>(gv.z), static_cast<uint32_t>(gv.w)};
+            uint32_t o[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) gnext[i] = *reinterpret_cast<const int4*>(g_row + (c + 1) * 32 + 8 * i);
-      }
-      tmem_ld_wait();
-      if (valid) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int4 gv = gcur[i];
-          const uint32_t gw[4] = {static_cast<uint32_t>(gv.x), static_cast<uint32_t>(gv.y),
-                                  static_cast<uint32_t>(gv.z), static_cast<uint32_t>(gv.w)};
-          uint32_t o[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float g0 = bf16_lo(gw[e]), g1 = bf16_hi(gw[e]);
-            // y is rounded to bf16 before the dot product, as a stored y would be.
-            const uint32_t yb = pack_bf16(__uint_as_float(r[8 * i + 2 * e]), __uint_as_float(r[8 * i + 2 * e + 1]));
-            partial += bf16_lo(yb) * g0 + bf16_hi(yb) * g1;
-            o[e] = pack_bf16(w * g0, w * g1);
+            for (int e = 0; e < 4; ++e) {
+              const float g0 = bf16_lo(gw[e]), g1 = bf16_hi(gw[e]);
+              // y is rounded to bf16 before the dot product, as a stored y would be.
+              const uint32_t yb = pack_bf16(__uint_as_float(r[8 * i + 2 * e]), __uint_as_float(r[8 * i + 2 * e + 1]));
+              partial += bf16_lo(yb) * g0 + bf16_hi(yb) * g1;
+              o[e] = pack_bf16(w * g0, w * g1);
+            }
+            stage_put(stage_gen, lane, c * 4 + i, make_int4(o[0], o[1], o[2], o[3]));
           }
-          *reinterpret_cast<int4*>(dy_row + c * 32 + 8 * i) = make_int4(o[0], o[1], o[2], o[3]);
         }
       }
+      stage_flush(stage_gen, lane, reinterpret_cast<uint8_t*>(p.out0 + block_off + half * 128),
+                  static_cast<size_t>(p.ld0) * 2, nvalid);
     }
     if (valid) p.dwp[static_cast<size_t>(grow) * p.dwp_tiles + tl.n] = partial;
   } else if constexpr (MODE == kModeDswiglu) {
+    if (p.stripe <= 64) {
+      // The tile's 512 striped columns of h / dh are four 128-column blocks; with stripes of 32 or 64 columns block b
+      // holds the gate and up values of exactly the accumulator columns [64 b, 64 b + 64). The warp brings a block of h
+      // into the staging buffer, every thread turns its own row into dh in place, the warp writes the block out.
+      const int nvalid = plan_clip(tl.nrows - q * 32, 0, 32);
+      const size_t block_off = static_cast<size_t>(tl.row0 + q * 32) * p.ld0 + 2 * tl.n * kBlockN;
+      const int s8 = p.stripe >> 3;  // 16-byte pieces per stripe
+      const uint8_t* h_block = reinterpret_cast<const uint8_t*>(p.in0 + block_off);
+      const size_t ld_bytes = static_cast<size_t>(p.ld0) * 2;
+      int4 fetched[16];
+      stage_fetch(fetched, lane, h_block, ld_bytes, nvalid);
+#pragma unroll 1
+      for (int b = 0; b < 4; ++b) {
+        stage_commit(stage_gen, lane, fetched);
+        // The next block's h values are requested now and used after this block has been written out.
+        if (b + 1 < 4) stage_fetch(fetched, lane, h_block + (b + 1) * 256, ld_bytes, nvalid);
+#pragma unroll 1
+        for (int hh = 0; hh < 2; ++hh) {  // 32 accumulator columns at a time
+          tmem_ld_32x32(tacc + b * 64 + hh * 32, r);
+          tmem_ld_wait();
+          __syncwarp();
+#pragma unroll
+          for (int i4 = 0; i4 < 4; ++i4) {  // eight accumulator columns at a time
+            if (!valid) break;
+            const uint32_t* acc = r + 8 * i4;
+            const int i = hh * 4 + i4;
+            const int gpiece = (i / s8) * 2 * s8 + (i % s8), upiece = gpiece + s8;
+            const int4 hg = stage_get(stage_gen, lane, gpiece), hu = stage_get(stage_gen, lane, upiece);
+            const uint32_t gw[4] = {static_cast<uint32_t>(hg.x), static_cast<uint32_t>(hg.y),
+                                    static_cast<uint32_t>(hg.z), static_cast<uint32_t>(hg.w)};
+            const uint32_t uw[4] = {static_cast<uint32_t>(hu.x), static_cast<uint32_t>(hu.y),
+                                    static_cast<uint32_t>(hu.z), static_cast<uint32_t>(hu.w)};
+            uint32_t og[4], ou[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              // d_act is rounded to bf16 first, as the unfused reference stores it.
+              const uint32_t db = pack_bf16(__uint_as_float(acc[2 * e]), __uint_as_float(acc[2 * e + 1]));
+              float dg[2], du[2];
+#pragma unroll
+              for (int z = 0; z < 2; ++z) {
+                const float d = z ? bf16_hi(db) : bf16_lo(db);
+                const float gt = z ? bf16_hi(gw[e]) : bf16_lo(gw[e]);
+                const float up = z ? bf16_hi(uw[e]) : bf16_lo(uw[e]);
+                const float sig = 1.0f / (1.0f + __expf(-gt));
+                const float sl = gt * sig;
+                dg[z] = d * up * (sig + sl * (1.0f - sig));
+                du[z] = d * sl;
+              }
+              og[e] = pack_bf16(dg[0], dg[1]);
+              ou[e] = pack_bf16(du[0], du[1]);
+            }
+            stage_put(stage_gen, lane, gpiece, make_int4(og[0], og[1], og[2], og[3]));
+            stage_put(stage_gen, lane, upiece, make_int4(ou[0], ou[1], ou[2], ou[3]));
+          }
+        }
+        stage_flush(stage_gen, lane, reinterpret_cast<uint8_t*>(p.out0 + block_off + b * 128),
+                    static_cast<size_t>(p.ld0) * 2, nvalid);
+      }
+      return;
+    }
+    // stripe 128: a block of dh needs two blocks of h; the rows are read and written directly, one chunk ahead.
     const __nv_bfloat16* h_row = p.in0 + static_cast<size_t>(grow) * p.ld0;
     __nv_bfloat16* dh_row = p.out0 + static_cast<size_t>(grow) * p.ld0;
     auto gate_col = [&](int c) {  // striped column of the gate values that belong to accumulator chunk c

@@ -53,8 +53,10 @@ __device__ __forceinline__ void issue_kblock(const GemmParams& p, const Tile& tl
 template <int MODE>
 constexpr int epilogue_warps() { return 4; }
 
+// 168 registers per thread: 192 threads x 168 leave half of the SM's register file to a 512-thread, 64-register copy
+// CTA (the dispatch put, the fp8 expansion), which has to become resident BESIDE this kernel for the overlap to happen.
 template <int MODE>
-__global__ void __launch_bounds__(64 + 32 * epilogue_warps<MODE>(), 1)
+__global__ void __maxnreg__(168)
 grouped_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c) {
   using Traits = ModeTraits<MODE>;

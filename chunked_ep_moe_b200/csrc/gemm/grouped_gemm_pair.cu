@@ -80,8 +80,10 @@ __device__ __forceinline__ void issue_pair_kblock(const GemmParams& p, const Til
   }
 }
 
+// 168 registers per thread: 192 threads x 168 leave half of the SM's register file to a 512-thread, 64-register copy
+// CTA (the dispatch put, the fp8 expansion), which has to become resident BESIDE this kernel for the overlap to happen.
 template <int MODE>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __maxnreg__(168)
 grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap map_a,
                          const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c) {
   using Traits = ModeTraits<MODE>;
