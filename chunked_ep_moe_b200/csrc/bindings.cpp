@@ -51,6 +51,26 @@ torch::Tensor plan_build_host(torch::Tensor counts, int64_t S, int64_t max_slice
   return plan;
 }
 
+// The plan kernel itself on a traffic matrix that is already complete in this GPU's memory (no peers to wait for):
+// what a rank's kernel computes once every row has landed.
+torch::Tensor plan_build_device(torch::Tensor counts, int64_t S, int64_t max_slices, int64_t me) {
+  TORCH_CHECK(counts.is_cuda() && counts.scalar_type() == torch::kInt32 && counts.dim() == 3 &&
+                  counts.size(0) == counts.size(1) && counts.is_contiguous(),
+              "counts must be a contiguous CUDA int32 [P, P, L] tensor");
+  const int P = static_cast<int>(counts.size(0)), L = static_cast<int>(counts.size(2));
+  TORCH_CHECK(me >= 0 && me < P, "rank out of range");
+  cem::PlanKernelParams p{};
+  p.lay = cem::make_plan_layout(P, L, static_cast<int>(S), static_cast<int>(max_slices));
+  torch::Tensor plan = torch::zeros({p.lay.total}, counts.options());
+  torch::Tensor mine = counts[me].contiguous();
+  p.me = static_cast<int>(me);
+  p.my_counts = mine.data_ptr<int>();
+  p.counts = counts.data_ptr<int>();
+  p.plan = plan.data_ptr<int>();
+  cem::launch_plan_build(p, at::cuda::getCurrentCUDAStream());
+  return plan;
+}
+
 int64_t arena_bytes(int P, int L, int S, int D, int tk_cap, bool fp8) {
   return static_cast<int64_t>(cem::make_arena_layout(P, L, S, D, tk_cap, fp8).total);
 }
@@ -79,6 +99,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "chunked expert-parallel MoE: sm_100a kernels and runtime";
   m.def("plan_layout", &plan_layout_dict, "offsets of the per-pass plan buffer");
   m.def("plan_build_host", &plan_build_host, "host build of the per-pass plan tables (CPU tests)");
+  m.def("plan_build_device", &plan_build_device, "the plan kernel on a complete traffic matrix (GPU tests)");
   m.def("arena_bytes", &arena_bytes, "size of one rank's symmetric arena");
   m.def("arena_alloc", &cem::arena_alloc);
   m.def("arena_free", &cem::arena_free);

@@ -7,6 +7,92 @@ namespace cem {
 
 namespace {
 
+// Exclusive prefix sum of `v` over the warp's lanes; `total` receives the warp's sum.
+__device__ __forceinline__ int warp_exclusive_scan(int v, int lane, int* total) {
+  int inc = v;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int up = __shfl_up_sync(0xffffffffu, inc, d);
+    if (lane >= d) inc += up;
+  }
+  *total = __shfl_sync(0xffffffffu, inc, 31);
+  return inc - v;
+}
+
+// Per-slice tables, one warp per slice (what `plan_phase_b` does with one thread per slice): lanes take the experts
+// (then the segments) 32 at a time and a warp scan numbers their tiles (their put chunks) in expert order.
+__device__ void plan_phase_b_warps(int* plan, const PlanLayout& y, const int* seg_start, const int* seg_size,
+                                   const int* send_start, const int* expert_start, const int* expert_rows) {
+  const int P = y.P, L = y.L, S = y.S, n = P * L;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  int num_slices = plan[0];
+  if (num_slices > y.max_slices) num_slices = y.max_slices;
+  for (int j = warp; j < y.max_slices; j += nwarps) {
+    int num_m = 0, num_g = 0, num_p = 0, chunks = 0;
+    if (j < num_slices) {
+      const int lo = j * S, hi = lo + S;
+      int* mt = plan + y.off_mtiles + 4 * y.max_mtiles * j;
+      int* gt = plan + y.off_gtiles + 4 * y.max_gtiles * j;
+      int* pt = plan + y.off_ptiles + 4 * y.max_ptiles * j;
+      for (int l0 = 0; l0 < L; l0 += 32) {
+        const int l = l0 + lane;
+        int es = 0, er = -1, first = 0, rows = 0;
+        if (l < L) {
+          es = expert_start[l];
+          er = expert_rows[l];
+          first = plan_clip(lo, es, es + er);
+          rows = plan_clip(hi, es, es + er) - first;
+        }
+        const int cm = (rows + kTileM - 1) / kTileM, cp = (rows + 2 * kTileM - 1) / (2 * kTileM);
+        const int cg = (rows > 0 || (j == 0 && er == 0)) ? 1 : 0;
+        int tm, tp, tg;
+        const int em = num_m + warp_exclusive_scan(cm, lane, &tm);
+        const int ep = num_p + warp_exclusive_scan(cp, lane, &tp);
+        const int eg = num_g + warp_exclusive_scan(cg, lane, &tg);
+        for (int t = 0; t < cm; ++t) {
+          const int off = t * kTileM;
+          reinterpret_cast<int4*>(mt)[em + t] =
+              make_int4(l, first - lo + off, rows - off < kTileM ? rows - off : kTileM, 0);
+        }
+        for (int t = 0; t < cp; ++t) {
+          const int off = t * 2 * kTileM;
+          reinterpret_cast<int4*>(pt)[ep + t] =
+              make_int4(l, first - lo + off, rows - off < 2 * kTileM ? rows - off : 2 * kTileM, 0);
+        }
+        if (cg) {
+          reinterpret_cast<int4*>(gt)[eg] =
+              rows > 0 ? make_int4(l, first - lo, rows, (es >= lo ? kGroupFirst : 0) | (es + er <= hi ? kGroupFinal : 0))
+                       : make_int4(l, 0, 0, kGroupFirst | kGroupFinal);
+        }
+        num_m += tm;
+        num_p += tp;
+        num_g += tg;
+      }
+      int* put = plan + y.off_put + 4 * n * j;
+      for (int i0 = 0; i0 < n; i0 += 32) {
+        const int i = i0 + lane;
+        int ss = 0, first = 0, size = 0;
+        if (i < n) {
+          ss = seg_start[i];
+          const int sz = seg_size[i];
+          first = plan_clip(lo, ss, ss + sz);
+          size = plan_clip(hi, ss, ss + sz) - first;
+        }
+        int tc;
+        const int ec = chunks + warp_exclusive_scan((size + kPutChunkRows - 1) / kPutChunkRows, lane, &tc);
+        if (i < n) reinterpret_cast<int4*>(put)[i] = make_int4(send_start[i] + (first - ss), size, first - lo, ec);
+        chunks += tc;
+      }
+    }
+    if (lane == 0) {
+      plan[y.off_num_mtiles + j] = num_m;
+      plan[y.off_num_gtiles + j] = num_g;
+      plan[y.off_num_chunks + j] = chunks;
+      plan[y.off_num_ptiles + j] = num_p;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256) plan_build_kernel(const PlanKernelParams p) {
   __shared__ int s_abort;
   const int P = p.lay.P, n = P * p.lay.L;
@@ -36,7 +122,34 @@ __global__ void __launch_bounds__(256) plan_build_kernel(const PlanKernelParams 
     if (threadIdx.x == 0) p.plan[0] = 0;  // zero slices: the pass launches nothing
     return;
   }
-  // 3. tables
+  // 3. tables. When the traffic matrix and the per-segment sums fit into shared memory (always, at real sizes) the block
+  // works from there and the per-slice tables are built a warp per slice; the arithmetic is `plan_phase_a/b`'s.
+  extern __shared__ int s_plan[];
+  if (p.use_smem) {
+    const int L = p.lay.L;
+    int* s_counts = s_plan;
+    for (int i = threadIdx.x; i < P * n; i += blockDim.x) s_counts[i] = p.counts[i];
+    __syncthreads();
+    plan_phase_a(s_counts, p.plan, p.lay, p.me, threadIdx.x, blockDim.x);
+    __syncthreads();
+    int* s_seg_start = s_counts + P * n;
+    int* s_seg_size = s_seg_start + n;
+    int* s_send_start = s_seg_size + n;
+    int* s_expert_start = s_send_start + n;
+    int* s_expert_rows = s_expert_start + L;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      s_seg_start[i] = p.plan[p.lay.off_seg_start + i];
+      s_seg_size[i] = p.plan[p.lay.off_seg_size + i];
+      s_send_start[i] = p.plan[p.lay.off_send_start + i];
+    }
+    for (int l = threadIdx.x; l < L; l += blockDim.x) {
+      s_expert_start[l] = p.plan[p.lay.off_expert_start + l];
+      s_expert_rows[l] = p.plan[p.lay.off_expert_rows + l];
+    }
+    __syncthreads();
+    plan_phase_b_warps(p.plan, p.lay, s_seg_start, s_seg_size, s_send_start, s_expert_start, s_expert_rows);
+    return;
+  }
   plan_phase_a(p.counts, p.plan, p.lay, p.me, threadIdx.x, blockDim.x);
   __syncthreads();
   plan_phase_b(p.plan, p.lay, threadIdx.x, blockDim.x);
@@ -122,8 +235,12 @@ __global__ void __launch_bounds__(kSortThreads) sort_scatter_kernel(const int* i
 
 }  // namespace
 
-void launch_plan_build(const PlanKernelParams& p, cudaStream_t stream) {
-  plan_build_kernel<<<1, 256, 0, stream>>>(p);
+void launch_plan_build(const PlanKernelParams& p_in, cudaStream_t stream) {
+  PlanKernelParams p = p_in;
+  const int n = p.lay.P * p.lay.L;
+  const size_t smem = sizeof(int) * (static_cast<size_t>(p.lay.P) * n + 3 * static_cast<size_t>(n) + 2 * p.lay.L);
+  p.use_smem = smem <= 40 * 1024 ? 1 : 0;  // 256 experts on 8 ranks need 11.5 KB; anything larger takes the serial path
+  plan_build_kernel<<<1, 256, p.use_smem ? smem : 0, stream>>>(p);
 }
 
 void plan_build_host(const int* counts, int* plan, const PlanLayout& lay, int me) {

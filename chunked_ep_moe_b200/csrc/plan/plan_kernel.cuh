@@ -22,6 +22,7 @@ struct PlanKernelParams {
   int* plan;                       // output tables
   uint32_t spin_limit;
   StatusBlock* status;
+  int use_smem = 0;                // set by the launcher: the tables are built from a shared-memory copy of the matrix
 };
 
 // Exchanges the [P, L] histograms (each rank stores its row into every peer and releases a flag),

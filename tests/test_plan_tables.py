@@ -120,3 +120,34 @@ def test_status_block_text():
     assert "pipeline barrier timed out" in ext.format_status([1, 1, 4, 17, 302, 0, 0, 9], 0)
     assert "expected 4294967295" in ext.format_status([2, 1, 0, 0, 0, -1, 0, 0], 0)  # counters are unsigned
     assert "malformed" in ext.format_status([1, 2], 0)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("P,L,S,tokens,top_k", [(1, 4, 16, 16, 2), (1, 256, 8192, 8192, 8), (4, 64, 8192, 8192, 8),
+                                                (8, 32, 8192, 8192, 8), (8, 4, 24, 16, 2), (3, 5, 7, 33, 3),
+                                                (2, 40, 100, 300, 4)])
+@pytest.mark.parametrize("skew", ["uniform", "all_one", "empty"])
+def test_plan_kernel_matches_host_tables(P, L, S, tokens, top_k, skew):
+    """The plan kernel (shared-memory copy of the matrix, one warp per slice) writes the host restatement's tables."""
+    ext = _build.load()
+    _, _, counts = _counts(P, L, tokens, top_k, skew, seed=P * 1000 + L)
+    counts = counts.to(torch.int32).contiguous()
+    max_slices = P * tokens * top_k // S + 2
+    lay = ext.plan_layout(P, L, S, max_slices)
+    n = P * L
+    for me in sorted({0, P - 1}):
+        host = ext.plan_build_host(counts, S, max_slices, me).numpy()
+        dev = ext.plan_build_device(counts.cuda(), S, max_slices, me).cpu().numpy()
+        header_and_sums = lay["num_mtiles"]  # header + the per-segment and per-expert sums
+        np.testing.assert_array_equal(dev[:header_and_sums], host[:header_and_sums])
+        for key in ("num_mtiles", "num_gtiles", "num_chunks", "num_ptiles"):
+            np.testing.assert_array_equal(dev[lay[key]: lay[key] + max_slices], host[lay[key]: lay[key] + max_slices])
+        for j in range(max_slices):
+            for key, cap, num in (("mtiles", lay["max_mtiles"], "num_mtiles"), ("gtiles", lay["max_gtiles"], "num_gtiles"),
+                                  ("ptiles", lay["max_ptiles"], "num_ptiles")):
+                used = 4 * host[lay[num] + j]
+                at = lay[key] + 4 * cap * j
+                np.testing.assert_array_equal(dev[at: at + used], host[at: at + used])
+            if j < host[0]:
+                at = lay["put"] + 4 * n * j
+                np.testing.assert_array_equal(dev[at: at + 4 * n], host[at: at + 4 * n])
