@@ -169,12 +169,9 @@ __device__ __forceinline__ void stage_commit(uint8_t* stage, int lane, const int
   __syncwarp();
 }
 
-__device__ __forceinline__ int4 pack8(const uint32_t* r8) {  // eight fp32 accumulator values -> eight bf16
-  return make_int4(pack_bf16(__uint_as_float(r8[0]), __uint_as_float(r8[1])),
-                   pack_bf16(__uint_as_float(r8[2]), __uint_as_float(r8[3])),
-                   pack_bf16(__uint_as_float(r8[4]), __uint_as_float(r8[5])),
-                   pack_bf16(__uint_as_float(r8[6]), __uint_as_float(r8[7])));
-}
+// SwiGLU' goes through the staging block when a tile has fewer k-blocks than this (measured: 32 k-blocks per tile and
+// below gain, 112 k-blocks per tile lose 3 % against the direct form with a one-chunk prefetch).
+constexpr int kStagedDswigluMaxKBlocks = 64;
 
 // Called by an epilogue warp BEFORE it waits for the tile's accumulator: asks L2 for the row-wise inputs the epilogue
 // will read (the output gradient's columns for the down -> d_weight mode, the gate/up pre-activations for the
@@ -215,9 +212,8 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
 
   if constexpr (MODE == kModeSwiglu) {
     uint32_t u[32];
-    const int nvalid = plan_clip(tl.nrows - q * 32, 0, 32);  // rows of this warp's 32 that belong to the tile
-    const size_t block_row = static_cast<size_t>(tl.row0 + q * 32);
-    // act: 128 columns = one 256-byte staging block
+    __nv_bfloat16* act_row = p.out0 + static_cast<size_t>(grow) * p.ld0 + tl.n * (kBlockN / 2);
+    __nv_bfloat16* h_row = p.out1 ? p.out1 + static_cast<size_t>(grow) * p.ld1 + tl.n * kBlockN : nullptr;
 #pragma unroll 1
     for (int c = 0; c < 4; ++c) {
       const int f_local = c * 32;
@@ -226,38 +222,32 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
       tmem_ld_32x32(tacc + gcol, r);
       tmem_ld_32x32(tacc + ucol, u);
       tmem_ld_wait();
-      uint32_t o[16];
+      if (valid) {
+        uint32_t o[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float g0 = __uint_as_float(r[2 * i]), g1 = __uint_as_float(r[2 * i + 1]);
-        const float u0 = __uint_as_float(u[2 * i]), u1 = __uint_as_float(u[2 * i + 1]);
-        o[i] = pack_bf16(silu_f(g0) * u0, silu_f(g1) * u1);
-      }
+        for (int i = 0; i < 16; ++i) {
+          const float g0 = __uint_as_float(r[2 * i]), g1 = __uint_as_float(r[2 * i + 1]);
+          const float u0 = __uint_as_float(u[2 * i]), u1 = __uint_as_float(u[2 * i + 1]);
+          o[i] = pack_bf16(silu_f(g0) * u0, silu_f(g1) * u1);
+        }
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        stage_put(stage_gen, lane, c * 4 + i, make_int4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]));
-    }
-    stage_flush(stage_gen, lane,
-                reinterpret_cast<uint8_t*>(p.out0 + block_row * p.ld0 + tl.n * (kBlockN / 2)),
-                static_cast<size_t>(p.ld0) * 2, nvalid);
-    if (p.out1 != nullptr) {
-      // h (backward remat): the accumulator's 256 columns ARE the tile's striped pre-activations; two 128-column blocks
-#pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
-#pragma unroll 1
-        for (int c = 0; c < 4; c += 2) {
-          tmem_ld_32x32(tacc + half * 128 + c * 32, r);
-          tmem_ld_32x32(tacc + half * 128 + c * 32 + 32, u);
-          tmem_ld_wait();
+        for (int i = 0; i < 4; ++i)
+          *reinterpret_cast<int4*>(act_row + f_local + 8 * i) = make_int4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+        if (h_row != nullptr) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            stage_put(stage_gen, lane, c * 4 + i, pack8(r + 8 * i));
-            stage_put(stage_gen, lane, c * 4 + 4 + i, pack8(u + 8 * i));
+            *reinterpret_cast<int4*>(h_row + gcol + 8 * i) =
+                make_int4(pack_bf16(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])),
+                          pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
+                          pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])),
+                          pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7])));
+            *reinterpret_cast<int4*>(h_row + ucol + 8 * i) =
+                make_int4(pack_bf16(__uint_as_float(u[8 * i]), __uint_as_float(u[8 * i + 1])),
+                          pack_bf16(__uint_as_float(u[8 * i + 2]), __uint_as_float(u[8 * i + 3])),
+                          pack_bf16(__uint_as_float(u[8 * i + 4]), __uint_as_float(u[8 * i + 5])),
+                          pack_bf16(__uint_as_float(u[8 * i + 6]), __uint_as_float(u[8 * i + 7])));
           }
         }
-        stage_flush(stage_gen, lane,
-                    reinterpret_cast<uint8_t*>(p.out1 + block_row * p.ld1 + tl.n * kBlockN + half * 128),
-                    static_cast<size_t>(p.ld1) * 2, nvalid);
       }
     }
   } else if constexpr (Traits::kCombine) {
@@ -366,7 +356,7 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
     }
     if (valid) p.dwp[static_cast<size_t>(grow) * p.dwp_tiles + tl.n] = partial;
   } else if constexpr (MODE == kModeDswiglu) {
-    if (p.stripe <= 64) {
+    if (p.stripe <= 64 && p.k_blocks < kStagedDswigluMaxKBlocks) {
       // The tile's 512 striped columns of h / dh are four 128-column blocks; with stripes of 32 or 64 columns block b
       // holds the gate and up values of exactly the accumulator columns [64 b, 64 b + 64). The warp brings a block of h
       // into the staging buffer, every thread turns its own row into dh in place, the warp writes the block out.
@@ -426,7 +416,8 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
       }
       return;
     }
-    // stripe 128: a block of dh needs two blocks of h; the rows are read and written directly, one chunk ahead.
+    // Deep contractions (the epilogue hides behind the next tile either way and this form is a little cheaper), and
+    // stripe 128 (a block of dh needs two blocks of h): the rows are read and written directly, one chunk ahead.
     const __nv_bfloat16* h_row = p.in0 + static_cast<size_t>(grow) * p.ld0;
     __nv_bfloat16* dh_row = p.out0 + static_cast<size_t>(grow) * p.ld0;
     auto gate_col = [&](int c) {  // striped column of the gate values that belong to accumulator chunk c
