@@ -55,6 +55,7 @@ struct GemmParams {
   int stripe;        // SwiGLU stripe width (swiglu / dswiglu)
   uint32_t spin_limit;   // polls of a cross-GPU flag before giving up
   uint32_t mbar_limit;   // microseconds a pipeline barrier may take before giving up
+  int suspend_waits;     // pair kernels: barriers completed from the partner CTA are waited for with try_wait, not polled
   StatusBlock* status;
   // Optional pipeline counters of this mode, [grid][kProfSlots] summed over launches; null = not counted.
   unsigned long long* prof;
@@ -103,6 +104,7 @@ static_assert(kGemmSmemBytes + 1024 + 1024 + 16 <= 233472, "no room for a second
 // of another kernel beside a persistent GEMM CTA; 1024 takes the SM's shared memory for the GEMM CTA alone (put and
 // expansion kernels then only run on SMs a GEMM CTA has left). A measurement knob (`CEM_GEMM_EXCLUSIVE_SM=1`).
 extern int g_gemm_extra_smem;
+extern int g_pair_suspend_waits;  // CEM_PAIR_SUSPEND: see GemmParams::suspend_waits
 
 // `map_c`: weight-gradient mode only, the bf16 gradient [L*M, N] with boxes of 32 rows x 64 columns (tiled stores);
 // the other modes ignore it (pass any valid map).

@@ -28,6 +28,12 @@ constexpr int kPairStageBytesB = (kBlockN / 2) * kBlockK * 2;  // 16 KB: this CT
 constexpr int kPairStageBytes = kPairStageBytesA + kPairStageBytesB;
 constexpr int kPairBand = kRasterBand / 2;                     // pairs swept together across N
 
+// Wait on a barrier that the partner CTA (its MMA commits, its relay warp) completes: polled or suspending.
+__device__ __forceinline__ bool pair_wait(int suspend, uint32_t bar, uint32_t parity, uint32_t limit_us,
+                                          const volatile int* abort = nullptr) {
+  return suspend ? mbar_wait(bar, parity, limit_us, abort) : mbar_wait_poll(bar, parity, limit_us, abort);
+}
+
 // Tile as seen by CTA `rank` of the pair.
 template <int MODE>
 __device__ __forceinline__ Tile decode_pair_tile(const GemmParams& p, int t, int num_entries, int rank) {
@@ -201,7 +207,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
         }
         for (int kb = 0; kb < tl.kblocks; ++kb) {
           const long long w0 = counting ? clock64() : 0;
-          const bool ok = __all_sync(0xffffffffu, mbar_wait_poll(empty_bar(ps), pph ^ 1u, p.mbar_limit, abort_flag));
+          const bool ok = __all_sync(0xffffffffu, pair_wait(p.suspend_waits, empty_bar(ps), pph ^ 1u, p.mbar_limit, abort_flag));
           if (!ok) {
             if (lane == 0) {
               report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1100 + ps, 0, 0);
@@ -287,7 +293,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
         bool ok = true;
         if (leader) {
           const long long w0 = counting ? clock64() : 0;
-          ok = __all_sync(0xffffffffu, mbar_wait_poll(acc_empty_bar(as), aph ^ 1u, p.mbar_limit, abort_flag));
+          ok = __all_sync(0xffffffffu, pair_wait(p.suspend_waits, acc_empty_bar(as), aph ^ 1u, p.mbar_limit, abort_flag));
           if (counting) acc_wait += clock64() - w0;
           if (!ok) { fail(t, 1200 + as); break; }
           tcgen05_fence_after_sync();
@@ -295,7 +301,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
         for (int kb = 0; kb < solo_kblocks; ++kb) {
           const long long w1 = counting ? clock64() : 0;
           ok = mbar_wait(full_bar(cs), cph, p.mbar_limit, abort_flag);
-          if (ok && kRelay && leader) ok = mbar_wait_poll(ready_bar(cs), cph, p.mbar_limit, abort_flag);
+          if (ok && kRelay && leader) ok = pair_wait(p.suspend_waits, ready_bar(cs), cph, p.mbar_limit, abort_flag);
           ok = __all_sync(0xffffffffu, ok);
           if (counting) full_wait += clock64() - w1;
           if (!ok) { fail(t, 1300 + cs); break; }
@@ -326,7 +332,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
             if (!leader) {
               if (elect_one()) mbar_arrive_cluster(map_to_cta(ready_bar(cs), peer));
             } else {
-              ok = __all_sync(0xffffffffu, mbar_wait_poll(ready_bar(cs), cph, p.mbar_limit, abort_flag));
+              ok = __all_sync(0xffffffffu, pair_wait(p.suspend_waits, ready_bar(cs), cph, p.mbar_limit, abort_flag));
               if (!ok) { fail(t, 1400 + cs); break; }
               tcgen05_fence_after_sync();
               issue_stage(cs, tmem_d, ksteps, kb == 0);
@@ -373,7 +379,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
       prefetch_epilogue_inputs<MODE>(p, tl, warp & 3, lane);
       const int as = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1u;
-      bool ok = mbar_wait_poll(acc_full_bar(as), aph, p.mbar_limit, abort_flag);
+      bool ok = pair_wait(p.suspend_waits, acc_full_bar(as), aph, p.mbar_limit, abort_flag);
       if (!ok) {
         report_status(p.status, kStatusMbarTimeout, kKernelGemm, MODE, t, 1500 + as, 0, 0);
         raise_abort();
@@ -429,9 +435,12 @@ int resident_pair_grid(Kernel kernel, int requested) {
 }  // namespace
 
 int g_pair_grid_used = 0;  // last pair grid size, for diagnostics
+int g_pair_suspend_waits = 0;
 
-void launch_grouped_gemm_pair(int mode, const GemmParams& p, const CUtensorMap& map_a, const CUtensorMap& map_b,
+void launch_grouped_gemm_pair(int mode, const GemmParams& p_in, const CUtensorMap& map_a, const CUtensorMap& map_b,
                               const CUtensorMap& map_c, int grid, cudaStream_t stream) {
+  GemmParams p = p_in;
+  p.suspend_waits = g_pair_suspend_waits;
   grid &= ~1;  // whole pairs only
 #define CEM_LAUNCH_PAIR(M)                                                                                       \
   case M: {                                                                                                      \

@@ -93,6 +93,7 @@ FusedRank::FusedRank(int P, int L, int me, int S, int D, int F, int K, int strip
   expect(!fp8 || D % 128 == 0, "fp8 wire needs D % 128 == 0");
   spin_limit_ = static_cast<uint32_t>(spin_limit);
   if (const char* v = std::getenv("CEM_GEMM_EXCLUSIVE_SM")) g_gemm_extra_smem = std::atoi(v) != 0 ? 1024 : 0;
+  if (const char* v = std::getenv("CEM_PAIR_SUSPEND")) g_pair_suspend_waits = std::atoi(v) != 0 ? 1 : 0;
   mbar_limit_ = 20u * 1000u * 1000u;  // microseconds: longer than any legitimate wait on another rank
   lay_ = make_plan_layout(P, L, S, max_slices);
   arena_lay_ = make_arena_layout(P, L, S, D, tk_cap, fp8);
