@@ -29,6 +29,7 @@ _SOURCES = [
     "plan/plan_kernel.cu",
     "plan/expert_sort_noalloc.cu",
     "model/model_kernels.cu",
+    "model/router_kernels.cu",
     "model/model_ops.cpp",
 ]
 _lock = threading.Lock()

@@ -8,6 +8,7 @@
 #include <string>
 
 #include "model_kernels.cuh"
+#include "router_kernels.cuh"
 
 namespace cem {
 
@@ -118,6 +119,47 @@ torch::Tensor cross_entropy_bwd(torch::Tensor logits, torch::Tensor targets, tor
                            grad_scale.data_ptr<float>(), dlogits.data_ptr(), static_cast<int>(logits.size(0)),
                            static_cast<int>(logits.size(1)), stream());
   return dlogits;
+}
+
+std::vector<torch::Tensor> router_fwd(torch::Tensor logits, torch::Tensor bias, int64_t top_k, double scaling) {
+  need(logits.is_cuda() && logits.scalar_type() == torch::kFloat32 && logits.dim() == 2 && logits.is_contiguous(),
+       "logits must be a contiguous CUDA fp32 [tokens, experts] matrix");
+  const int T = static_cast<int>(logits.size(0)), E = static_cast<int>(logits.size(1));
+  need(router_supported(E, static_cast<int>(top_k)), "router kernel needs experts % 32 == 0, experts <= 256, top_k <= 32");
+  need(bias.is_cuda() && bias.scalar_type() == torch::kFloat32 && bias.is_contiguous() && bias.numel() == E,
+       "bias must be a contiguous CUDA fp32 vector of `experts` elements");
+  const c10::cuda::CUDAGuard guard(logits.device());
+  auto i32 = logits.options().dtype(torch::kInt32);
+  torch::Tensor ids = torch::empty({T, top_k}, i32);
+  torch::Tensor weights = torch::empty({T, top_k}, logits.options());
+  torch::Tensor counts = torch::zeros({E}, i32);
+  torch::Tensor partial = torch::empty({router_blocks(T), E}, logits.options());
+  launch_router_fwd(logits.data_ptr<float>(), bias.data_ptr<float>(), ids.data_ptr<int>(), weights.data_ptr<float>(),
+                    counts.data_ptr<int>(), partial.data_ptr<float>(), T, E, static_cast<int>(top_k),
+                    static_cast<float>(scaling), stream());
+  return {ids, weights, counts, partial};
+}
+
+torch::Tensor router_bwd(torch::Tensor logits, torch::Tensor ids, torch::Tensor d_weights, torch::Tensor d_prob,
+                         double scaling) {
+  need(logits.is_cuda() && logits.scalar_type() == torch::kFloat32 && logits.dim() == 2 && logits.is_contiguous(),
+       "logits must be a contiguous CUDA fp32 [tokens, experts] matrix");
+  const int T = static_cast<int>(logits.size(0)), E = static_cast<int>(logits.size(1));
+  need(ids.is_cuda() && ids.scalar_type() == torch::kInt32 && ids.is_contiguous() && ids.dim() == 2 && ids.size(0) == T,
+       "ids must be a contiguous CUDA int32 [tokens, top_k] matrix");
+  const int top_k = static_cast<int>(ids.size(1));
+  need(router_supported(E, top_k), "router kernel needs experts % 32 == 0, experts <= 256, top_k <= 32");
+  need(d_weights.is_cuda() && d_weights.scalar_type() == torch::kFloat32 && d_weights.is_contiguous() &&
+           d_weights.numel() == static_cast<int64_t>(T) * top_k,
+       "d_weights must be a contiguous CUDA fp32 [tokens, top_k] matrix");
+  need(d_prob.is_cuda() && d_prob.scalar_type() == torch::kFloat32 && d_prob.is_contiguous() && d_prob.numel() == E,
+       "d_prob must be a contiguous CUDA fp32 vector of `experts` elements");
+  const c10::cuda::CUDAGuard guard(logits.device());
+  torch::Tensor d_logits = torch::empty_like(logits);
+  launch_router_bwd(logits.data_ptr<float>(), ids.data_ptr<int>(), d_weights.data_ptr<float>(),
+                    d_prob.data_ptr<float>(), d_logits.data_ptr<float>(), T, E, top_k, static_cast<float>(scaling),
+                    stream());
+  return d_logits;
 }
 
 }  // namespace cem

@@ -22,4 +22,10 @@ std::vector<torch::Tensor> cross_entropy_fwd(torch::Tensor logits, torch::Tensor
 torch::Tensor cross_entropy_bwd(torch::Tensor logits, torch::Tensor targets, torch::Tensor lse,
                                 torch::Tensor grad_scale);
 
+// Sigmoid top-k router on fp32 logits [T, E]: (ids [T, K] int32, weights [T, K], counts [E] int32, per-block score
+// sums [blocks, E]); backward: gradients of weights and of the score sums -> gradient of the logits.
+std::vector<torch::Tensor> router_fwd(torch::Tensor logits, torch::Tensor bias, int64_t top_k, double scaling);
+torch::Tensor router_bwd(torch::Tensor logits, torch::Tensor ids, torch::Tensor d_weights, torch::Tensor d_prob,
+                         double scaling);
+
 }  // namespace cem

@@ -27,7 +27,7 @@ import torch.nn.functional as F
 
 from ..api import chunked_moe
 from ..config import ChunkedMoEConfig
-from .fused_ops import add_rms_norm, cross_entropy, rope_qkv
+from .fused_ops import add_rms_norm, cross_entropy, rope_qkv, router_select
 
 
 @dataclasses.dataclass
@@ -131,19 +131,15 @@ class Router(nn.Module):
 
     def forward(self, x):
         cfg = self.cfg
-        scores = torch.sigmoid(F.linear(x.float(), self.weight.float()))  # [T, E]
-        _, ids = torch.topk(scores + self.routed_bias, cfg.top_k, dim=-1)
-        chosen = torch.gather(scores, 1, ids)
-        weights = chosen / chosen.sum(-1, keepdim=True).clamp_min(1e-20) * cfg.routed_scaling
-        # Load-balance loss: E * sum_i f_i * P_i with f_i the routed fraction and P_i the mean normalised score.
+        logits = F.linear(x.float(), self.weight.float())  # [T, E] fp32
+        ids, weights, counts, score_sums = router_select(logits, self.routed_bias, cfg.top_k, cfg.routed_scaling)
         with torch.no_grad():
-            counts = torch.zeros(cfg.num_experts, device=x.device).index_add_(
-                0, ids.reshape(-1), torch.ones(ids.numel(), device=x.device))
             self.load_counts += counts
-        frac = counts / max(ids.numel(), 1)
-        prob = (scores / scores.sum(-1, keepdim=True).clamp_min(1e-20)).mean(0)
+        # Load-balance loss: E * sum_i f_i * P_i with f_i the routed fraction and P_i the mean normalised score.
+        frac = counts.float() / max(ids.numel(), 1)
+        prob = score_sums / max(ids.shape[0], 1)
         aux = cfg.aux_loss_coef * cfg.num_experts * (frac * prob).sum()
-        return ids.to(torch.int32), weights, aux
+        return ids, weights, aux
 
     @torch.no_grad()
     def update_bias(self, group=None):

@@ -1,5 +1,5 @@
 """Fused CUDA ops of the decoder around the MoE layers: residual add + RMSNorm, rotary embedding straight out of the
-qkv projection, and the cross-entropy of bf16 logits. Each is one kernel per direction (`csrc/model/`) instead of a
+qkv projection, the cross-entropy of bf16 logits, and the sigmoid top-k router (everything after its logits GEMM). Each is one kernel per direction (`csrc/model/`) instead of a
 chain of framework elementwise kernels, which took a third of a trainer step's device time. On CPU tensors (and for
 dtypes other than bf16) the same functions fall back to plain torch ops with identical semantics, so the model code
 has one path. The reference ships no model code; these serve `models/deepseek_tiny.py`.
@@ -106,3 +106,46 @@ def cross_entropy(logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
     if _fusable(logits) and logits.shape[-1] % 8 == 0:
         return _CrossEntropy.apply(logits.contiguous(), targets.contiguous().long())
     return F.cross_entropy(logits.float(), targets)
+
+
+class _RouterSelect(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, bias, top_k, scaling):
+        ids, weights, counts, partial = _ext().router_fwd(logits, bias, top_k, scaling)
+        ctx.save_for_backward(logits, ids)
+        ctx.scaling = scaling
+        ctx.mark_non_differentiable(ids, counts)
+        return ids, weights, counts, partial.sum(0)
+
+    @staticmethod
+    def backward(ctx, _ids, d_weights, _counts, d_score_sums):
+        logits, ids = ctx.saved_tensors
+        if d_weights is None:
+            d_weights = torch.zeros(ids.shape, dtype=torch.float32, device=logits.device)
+        if d_score_sums is None:
+            d_score_sums = torch.zeros(logits.shape[1], dtype=torch.float32, device=logits.device)
+        d_logits = _ext().router_bwd(logits, ids, d_weights.contiguous().float(), d_score_sums.contiguous().float(),
+                                     ctx.scaling)
+        return d_logits, None, None, None
+
+
+def router_select(logits: torch.Tensor, bias: torch.Tensor, top_k: int,
+                  scaling: float) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Sigmoid top-k routing from fp32 `logits [T, E]`: `(ids [T, K] int32, weights [T, K], counts [E], score_sums [E])`.
+
+    Experts are chosen by `sigmoid(logits) + bias` (the bias takes part in the selection only), `weights` are the chosen
+    sigmoid scores normalised over the chosen and multiplied by `scaling`, `counts` the tokens per expert, and
+    `score_sums[e]` the sum over tokens of `score[t, e] / sum_e' score[t, e']` (its mean is the balance loss's P_e).
+    `weights` and `score_sums` are differentiable w.r.t. `logits`.
+    """
+    num_experts = logits.shape[1]
+    if (logits.is_cuda and logits.dtype == torch.float32 and num_experts % 32 == 0 and num_experts <= 256
+            and top_k <= 32):
+        return _RouterSelect.apply(logits.contiguous(), bias.float().contiguous(), top_k, float(scaling))
+    scores = torch.sigmoid(logits.float())
+    _, ids = torch.topk(scores + bias, top_k, dim=-1)
+    chosen = torch.gather(scores, 1, ids)
+    weights = chosen / chosen.sum(-1, keepdim=True).clamp_min(1e-20) * scaling
+    counts = torch.bincount(ids.reshape(-1), minlength=num_experts)
+    score_sums = (scores / scores.sum(-1, keepdim=True).clamp_min(1e-20)).sum(0)
+    return ids.to(torch.int32), weights, counts, score_sums

@@ -1,4 +1,4 @@
-"""The decoder's fused CUDA ops (residual add + RMSNorm, rotary embedding out of qkv, cross-entropy of bf16 logits)
+"""The decoder's fused CUDA ops (residual add + RMSNorm, rotary embedding out of qkv, cross-entropy of bf16 logits, router)
 against plain PyTorch fp32 references of the same ops, forward and backward."""
 
 import pytest
@@ -80,3 +80,45 @@ def test_cross_entropy(rows, cols):
     (want * 1.7).backward()
     assert abs(float(loss) - float(want)) <= 1e-3 * max(1.0, abs(float(want)))
     _close(logits.grad, ref.grad, "dlogits", 1e-2)
+
+
+@pytest.mark.parametrize("tokens,experts,top_k", [(1000, 64, 6), (8192, 256, 8), (7, 32, 1), (333, 96, 5)])
+def test_router_select(tokens, experts, top_k):
+    """Selection, weights, load counts, score sums and the gradient w.r.t. the logits against fp64 torch ops."""
+    gen = torch.Generator(device="cuda").manual_seed(tokens + experts)
+    logits = torch.randn(tokens, experts, generator=gen, device="cuda").requires_grad_(True)
+    bias = 0.1 * torch.randn(experts, generator=gen, device="cuda")
+    gw = torch.randn(tokens, top_k, generator=gen, device="cuda")
+    gs = torch.randn(experts, generator=gen, device="cuda")
+    scaling = 2.5
+    ids, weights, counts, sums = fused_ops.router_select(logits, bias, top_k, scaling)
+    ((weights * gw).sum() + (sums * gs).sum()).backward()
+    assert ids.dtype == torch.int32 and tuple(ids.shape) == (tokens, top_k)
+
+    ref_logits = logits.detach().double().requires_grad_(True)
+    scores = torch.sigmoid(ref_logits)
+    keys = (scores + bias.double()).detach()
+    picked = torch.gather(keys, 1, ids.long())
+    # a valid top-k: distinct experts, in descending order of score + bias, none of the others beats the last one
+    assert (torch.sort(ids.long(), dim=1).values.diff(dim=1) > 0).all() or top_k == 1
+    assert (picked.diff(dim=1) <= 1e-6).all()
+    rest = keys.scatter(1, ids.long(), float("-inf"))
+    assert (rest.max(dim=1).values <= picked[:, -1] + 1e-6).all()
+    chosen = torch.gather(scores, 1, ids.long())
+    ref_weights = chosen / chosen.sum(-1, keepdim=True).clamp_min(1e-20) * scaling
+    ref_sums = (scores / scores.sum(-1, keepdim=True).clamp_min(1e-20)).sum(0)
+    ((ref_weights * gw.double()).sum() + (ref_sums * gs.double()).sum()).backward()
+    torch.testing.assert_close(weights.double(), ref_weights.detach(), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(counts.long(), torch.bincount(ids.long().reshape(-1), minlength=experts))
+    torch.testing.assert_close(sums.double(), ref_sums.detach(), rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(logits.grad.double(), ref_logits.grad, rtol=1e-4, atol=1e-6)
+
+
+def test_router_select_is_deterministic():
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    logits = torch.randn(4096, 64, generator=gen, device="cuda")
+    bias = torch.zeros(64, device="cuda")
+    a = fused_ops.router_select(logits, bias, 6, 1.0)
+    b = fused_ops.router_select(logits, bias, 6, 1.0)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
