@@ -47,6 +47,7 @@ def main():
         argv += ["--slice-size", str(opts.slice_size)]
     args = trainer.build_parser().parse_args(argv)
     torch.cuda.set_device(0)
+    trainer.use_tf32_for_fp32_matmuls()
     cfg = trainer.model_config(args)
     model = DeepSeekTiny(cfg, None).to(device="cuda", dtype=torch.bfloat16)
     model.init_weights(0, 0)

@@ -120,6 +120,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rope_qkv_bwd", &cem::rope_qkv_bwd, "gradients of q, k, v -> gradient of qkv");
   m.def("cross_entropy_fwd", &cem::cross_entropy_fwd, "bf16 logits -> (loss per row, log-sum-exp per row)");
   m.def("cross_entropy_bwd", &cem::cross_entropy_bwd, "-> bf16 gradient of the logits");
+  m.def("dense_swiglu_fwd", &cem::dense_swiglu_fwd, "[gate | up] -> silu(gate) * up");
+  m.def("dense_swiglu_bwd", &cem::dense_swiglu_bwd, "-> gradient of [gate | up]");
   m.def("router_fwd", &cem::router_fwd, "fp32 logits, bias -> (ids, weights, counts, per-block score sums)");
   m.def("router_bwd", &cem::router_bwd, "-> fp32 gradient of the logits");
   py::class_<cem::KernelRunner>(m, "KernelRunner")

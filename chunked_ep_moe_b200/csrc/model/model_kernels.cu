@@ -280,6 +280,61 @@ __global__ void __launch_bounds__(256) cross_entropy_bwd_kernel(const __nv_bfloa
   }
 }
 
+// act = silu(gate) * up for gu = [gate | up] (two contiguous halves of `ffn` columns per row), eight columns a thread.
+__global__ void __launch_bounds__(256) dense_swiglu_fwd_kernel(const __nv_bfloat16* gu, __nv_bfloat16* act,
+                                                               size_t units, int ffn_units) {
+  for (size_t u = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; u < units;
+       u += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t row = u / ffn_units, c = u - row * ffn_units;
+    const int4 g = reinterpret_cast<const int4*>(gu)[row * 2 * ffn_units + c];
+    const int4 v = reinterpret_cast<const int4*>(gu)[row * 2 * ffn_units + ffn_units + c];
+    const uint32_t gw[4] = {(uint32_t)g.x, (uint32_t)g.y, (uint32_t)g.z, (uint32_t)g.w};
+    const uint32_t vw[4] = {(uint32_t)v.x, (uint32_t)v.y, (uint32_t)v.z, (uint32_t)v.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float g0 = bf_lo(gw[e]), g1 = bf_hi(gw[e]);
+      o[e] = bf_pack(g0 / (1.0f + __expf(-g0)) * bf_lo(vw[e]), g1 / (1.0f + __expf(-g1)) * bf_hi(vw[e]));
+    }
+    reinterpret_cast<int4*>(act)[u] = make_int4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// d_gu = [d_act * up * silu'(gate) | d_act * silu(gate)].
+__global__ void __launch_bounds__(256) dense_swiglu_bwd_kernel(const __nv_bfloat16* gu, const __nv_bfloat16* d_act,
+                                                               __nv_bfloat16* d_gu, size_t units, int ffn_units) {
+  for (size_t u = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; u < units;
+       u += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t row = u / ffn_units, c = u - row * ffn_units;
+    const size_t gi = row * 2 * ffn_units + c, vi = gi + ffn_units;
+    const int4 g = reinterpret_cast<const int4*>(gu)[gi];
+    const int4 v = reinterpret_cast<const int4*>(gu)[vi];
+    const int4 d = reinterpret_cast<const int4*>(d_act)[u];
+    const uint32_t gw[4] = {(uint32_t)g.x, (uint32_t)g.y, (uint32_t)g.z, (uint32_t)g.w};
+    const uint32_t vw[4] = {(uint32_t)v.x, (uint32_t)v.y, (uint32_t)v.z, (uint32_t)v.w};
+    const uint32_t dw[4] = {(uint32_t)d.x, (uint32_t)d.y, (uint32_t)d.z, (uint32_t)d.w};
+    uint32_t og[4], ov[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float dg[2], dv[2];
+#pragma unroll
+      for (int z = 0; z < 2; ++z) {
+        const float gt = z ? bf_hi(gw[e]) : bf_lo(gw[e]);
+        const float up = z ? bf_hi(vw[e]) : bf_lo(vw[e]);
+        const float da = z ? bf_hi(dw[e]) : bf_lo(dw[e]);
+        const float sig = 1.0f / (1.0f + __expf(-gt));
+        const float sl = gt * sig;
+        dg[z] = da * up * (sig + sl * (1.0f - sig));
+        dv[z] = da * sl;
+      }
+      og[e] = bf_pack(dg[0], dg[1]);
+      ov[e] = bf_pack(dv[0], dv[1]);
+    }
+    reinterpret_cast<int4*>(d_gu)[gi] = make_int4(og[0], og[1], og[2], og[3]);
+    reinterpret_cast<int4*>(d_gu)[vi] = make_int4(ov[0], ov[1], ov[2], ov[3]);
+  }
+}
+
 }  // namespace
 
 void launch_add_rms_norm_fwd(const void* x, const void* delta, const void* w, void* s_out, void* y, float* rstd,
@@ -340,6 +395,21 @@ void launch_cross_entropy_bwd(const void* logits, const int64_t* targets, const 
                               void* dlogits, int rows, int cols, cudaStream_t stream) {
   cross_entropy_bwd_kernel<<<rows, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), targets, lse,
                                                      grad_scale, static_cast<__nv_bfloat16*>(dlogits), cols);
+}
+
+void launch_dense_swiglu(const void* gu, const void* d_act, void* out, int rows, int ffn, bool backward,
+                         cudaStream_t stream) {
+  const size_t units = static_cast<size_t>(rows) * (ffn >> 3);
+  if (units == 0) return;
+  int grid = static_cast<int>((units + 255) / 256);
+  if (grid > 148 * 16) grid = 148 * 16;
+  if (backward)
+    dense_swiglu_bwd_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(gu),
+                                                      static_cast<const __nv_bfloat16*>(d_act),
+                                                      static_cast<__nv_bfloat16*>(out), units, ffn >> 3);
+  else
+    dense_swiglu_fwd_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(gu),
+                                                      static_cast<__nv_bfloat16*>(out), units, ffn >> 3);
 }
 
 }  // namespace cem

@@ -25,4 +25,9 @@ void launch_cross_entropy_fwd(const void* logits, const int64_t* targets, float*
 void launch_cross_entropy_bwd(const void* logits, const int64_t* targets, const float* lse, const float* grad_scale,
                               void* dlogits, int rows, int cols, cudaStream_t stream);
 
+// bf16 gu [rows, 2*ffn] = [gate | up], ffn a multiple of 8. Forward: out = silu(gate) * up, [rows, ffn] (`d_act` unused).
+// Backward: out = d_gu [rows, 2*ffn] from `d_act` [rows, ffn].
+void launch_dense_swiglu(const void* gu, const void* d_act, void* out, int rows, int ffn, bool backward,
+                         cudaStream_t stream);
+
 }  // namespace cem

@@ -121,6 +121,26 @@ torch::Tensor cross_entropy_bwd(torch::Tensor logits, torch::Tensor targets, tor
   return dlogits;
 }
 
+torch::Tensor dense_swiglu_fwd(torch::Tensor gu) {
+  need(bf16_matrix(gu) && gu.size(1) % 16 == 0, "gu must be a contiguous CUDA bf16 [rows, 2*ffn] matrix, ffn % 8 == 0");
+  const c10::cuda::CUDAGuard guard(gu.device());
+  torch::Tensor act = torch::empty({gu.size(0), gu.size(1) / 2}, gu.options());
+  launch_dense_swiglu(gu.data_ptr(), nullptr, act.data_ptr(), static_cast<int>(gu.size(0)),
+                      static_cast<int>(gu.size(1) / 2), false, stream());
+  return act;
+}
+
+torch::Tensor dense_swiglu_bwd(torch::Tensor gu, torch::Tensor d_act) {
+  need(bf16_matrix(gu) && gu.size(1) % 16 == 0, "gu must be a contiguous CUDA bf16 [rows, 2*ffn] matrix, ffn % 8 == 0");
+  need(bf16_matrix(d_act) && d_act.size(0) == gu.size(0) && d_act.size(1) * 2 == gu.size(1),
+       "d_act must be a contiguous CUDA bf16 [rows, ffn] matrix");
+  const c10::cuda::CUDAGuard guard(gu.device());
+  torch::Tensor d_gu = torch::empty_like(gu);
+  launch_dense_swiglu(gu.data_ptr(), d_act.data_ptr(), d_gu.data_ptr(), static_cast<int>(gu.size(0)),
+                      static_cast<int>(gu.size(1) / 2), true, stream());
+  return d_gu;
+}
+
 std::vector<torch::Tensor> router_fwd(torch::Tensor logits, torch::Tensor bias, int64_t top_k, double scaling) {
   need(logits.is_cuda() && logits.scalar_type() == torch::kFloat32 && logits.dim() == 2 && logits.is_contiguous(),
        "logits must be a contiguous CUDA fp32 [tokens, experts] matrix");

@@ -22,6 +22,9 @@ std::vector<torch::Tensor> cross_entropy_fwd(torch::Tensor logits, torch::Tensor
 torch::Tensor cross_entropy_bwd(torch::Tensor logits, torch::Tensor targets, torch::Tensor lse,
                                 torch::Tensor grad_scale);
 
+// silu(gate) * up of gu = [gate | up] (bf16 [rows, 2*ffn]) and its backward (-> d_gu).
+torch::Tensor dense_swiglu_fwd(torch::Tensor gu);
+torch::Tensor dense_swiglu_bwd(torch::Tensor gu, torch::Tensor d_act);
 // Sigmoid top-k router on fp32 logits [T, E]: (ids [T, K] int32, weights [T, K], counts [E] int32, per-block score
 // sums [blocks, E]); backward: gradients of weights and of the score sums -> gradient of the logits.
 std::vector<torch::Tensor> router_fwd(torch::Tensor logits, torch::Tensor bias, int64_t top_k, double scaling);

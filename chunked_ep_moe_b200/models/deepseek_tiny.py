@@ -27,7 +27,7 @@ import torch.nn.functional as F
 
 from ..api import chunked_moe
 from ..config import ChunkedMoEConfig
-from .fused_ops import add_rms_norm, cross_entropy, rope_qkv, router_select
+from .fused_ops import add_rms_norm, cross_entropy, dense_swiglu, rope_qkv, router_select
 
 
 @dataclasses.dataclass
@@ -104,8 +104,7 @@ class DenseSwiGLU(nn.Module):
         self.down = nn.Linear(ffn, dim, bias=False)
 
     def forward(self, x):
-        gate, up = self.gate_up(x).chunk(2, dim=-1)
-        return self.down(F.silu(gate) * up)
+        return self.down(dense_swiglu(self.gate_up(x)))
 
 
 class Router(nn.Module):

@@ -1,5 +1,5 @@
 """Fused CUDA ops of the decoder around the MoE layers: residual add + RMSNorm, rotary embedding straight out of the
-qkv projection, the cross-entropy of bf16 logits, and the sigmoid top-k router (everything after its logits GEMM). Each is one kernel per direction (`csrc/model/`) instead of a
+qkv projection, the cross-entropy of bf16 logits, the sigmoid top-k router (everything after its logits GEMM) and the dense SwiGLU. Each is one kernel per direction (`csrc/model/`) instead of a
 chain of framework elementwise kernels, which took a third of a trainer step's device time. On CPU tensors (and for
 dtypes other than bf16) the same functions fall back to plain torch ops with identical semantics, so the model code
 has one path. The reference ships no model code; these serve `models/deepseek_tiny.py`.
@@ -149,3 +149,25 @@ def router_select(logits: torch.Tensor, bias: torch.Tensor, top_k: int,
     counts = torch.bincount(ids.reshape(-1), minlength=num_experts)
     score_sums = (scores / scores.sum(-1, keepdim=True).clamp_min(1e-20)).sum(0)
     return ids.to(torch.int32), weights, counts, score_sums
+
+
+class _DenseSwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate_up):
+        ctx.save_for_backward(gate_up)
+        return _ext().dense_swiglu_fwd(gate_up)
+
+    @staticmethod
+    def backward(ctx, d_act):
+        (gate_up,) = ctx.saved_tensors
+        return _ext().dense_swiglu_bwd(gate_up, d_act.contiguous())
+
+
+def dense_swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """`silu(gate) * up` for `gate_up = [..., gate | up]` (two halves of the last dimension), one kernel per direction."""
+    ffn = gate_up.shape[-1] // 2
+    if _fusable(gate_up) and ffn % 8 == 0 and gate_up.shape[-1] == 2 * ffn:
+        flat = gate_up.reshape(-1, 2 * ffn).contiguous()
+        return _DenseSwiGLU.apply(flat).reshape(*gate_up.shape[:-1], ffn)
+    gate, up = gate_up.chunk(2, dim=-1)
+    return F.silu(gate) * up

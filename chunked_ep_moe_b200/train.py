@@ -89,7 +89,15 @@ def reduce_gradients(model: DeepSeekTiny, world: int, group=None) -> None:
             p.grad /= world
 
 
+def use_tf32_for_fp32_matmuls() -> None:
+    """The model's only fp32 matmuls are the router's logits and their backward. In the forward both operands are bf16
+    values widened to fp32, which TF32 holds exactly, so the tensor-core TF32 GEMM forms the same products as the SIMT
+    fp32 GEMM (accumulation stays fp32) in a fraction of its time."""
+    torch.backends.cuda.matmul.allow_tf32 = True
+
+
 def train(args, group=None) -> dict:
+    use_tf32_for_fp32_matmuls()
     distributed = dist.is_available() and dist.is_initialized()
     world = dist.get_world_size(group) if distributed else 1
     rank = dist.get_rank(group) if distributed else 0

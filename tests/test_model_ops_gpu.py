@@ -122,3 +122,18 @@ def test_router_select_is_deterministic():
     b = fused_ops.router_select(logits, bias, 6, 1.0)
     for x, y in zip(a, b):
         assert torch.equal(x, y)
+
+
+@pytest.mark.parametrize("rows,ffn", [(300, 512), (8192, 2048), (5, 8)])
+def test_dense_swiglu(rows, ffn):
+    gen = torch.Generator(device="cuda").manual_seed(rows)
+    gu = torch.randn(rows, 2 * ffn, device="cuda", generator=gen).bfloat16().requires_grad_(True)
+    go = torch.randn(rows, ffn, device="cuda", generator=gen).bfloat16()
+    out = fused_ops.dense_swiglu(gu)
+    out.backward(go)
+    ref_in = gu.detach().float().requires_grad_(True)
+    gate, up = ref_in.chunk(2, dim=-1)
+    ref = F.silu(gate) * up
+    ref.backward(go.float())
+    _close(out, ref, "act", 1e-2)
+    _close(gu.grad, ref_in.grad, "d_gate_up", 1e-2)
