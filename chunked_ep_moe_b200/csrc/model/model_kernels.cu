@@ -294,7 +294,8 @@ __global__ void __launch_bounds__(256) dense_swiglu_fwd_kernel(const __nv_bfloat
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float g0 = bf_lo(gw[e]), g1 = bf_hi(gw[e]);
-      o[e] = bf_pack(g0 / (1.0f + __expf(-g0)) * bf_lo(vw[e]), g1 / (1.0f + __expf(-g1)) * bf_hi(vw[e]));
+      o[e] = bf_pack(g0 * __fdividef(1.0f, 1.0f + __expf(-g0)) * bf_lo(vw[e]),
+                     g1 * __fdividef(1.0f, 1.0f + __expf(-g1)) * bf_hi(vw[e]));
     }
     reinterpret_cast<int4*>(act)[u] = make_int4(o[0], o[1], o[2], o[3]);
   }
@@ -322,7 +323,7 @@ __global__ void __launch_bounds__(256) dense_swiglu_bwd_kernel(const __nv_bfloat
         const float gt = z ? bf_hi(gw[e]) : bf_lo(gw[e]);
         const float up = z ? bf_hi(vw[e]) : bf_lo(vw[e]);
         const float da = z ? bf_hi(dw[e]) : bf_lo(dw[e]);
-        const float sig = 1.0f / (1.0f + __expf(-gt));
+        const float sig = __fdividef(1.0f, 1.0f + __expf(-gt));
         const float sl = gt * sig;
         dg[z] = da * up * (sig + sl * (1.0f - sig));
         dv[z] = da * sl;
