@@ -150,3 +150,27 @@ def test_router_balancing_state_survives_a_bf16_cast():
     router.update_bias()
     moved = (router.routed_bias - 0.5).abs()
     assert torch.allclose(moved, torch.full_like(moved, cfg.bias_update_rate), rtol=1e-3), moved
+
+
+def test_router_select_and_dense_swiglu_on_cpu():
+    """The plain-torch branches of the fused decoder ops: what the router and the dense FFN compute, written out."""
+    from chunked_ep_moe_b200.models import fused_ops
+
+    gen = torch.Generator().manual_seed(3)
+    logits = torch.randn(50, 12, generator=gen, requires_grad=True)
+    bias = torch.zeros(12)
+    bias[7] = 10.0  # the bias decides the selection but never enters the weights
+    ids, weights, counts, score_sums = fused_ops.router_select(logits, bias, 3, 2.0)
+    assert ids.dtype == torch.int32 and (ids[:, 0] == 7).all()
+    scores = torch.sigmoid(logits.detach())
+    chosen = torch.gather(scores, 1, ids.long())
+    torch.testing.assert_close(weights.detach(), 2.0 * chosen / chosen.sum(-1, keepdim=True))
+    torch.testing.assert_close(weights.sum(-1).detach(), torch.full((50,), 2.0))
+    assert int(counts.sum()) == 150 and int(counts[7]) == 50
+    torch.testing.assert_close(score_sums.sum().detach(), torch.tensor(50.0))  # normalised scores sum to 1 per token
+    (weights.sum() + score_sums[0]).backward()
+    assert torch.isfinite(logits.grad).all() and logits.grad.abs().sum() > 0
+
+    gu = torch.randn(9, 32, generator=gen)
+    gate, up = gu.chunk(2, dim=-1)
+    torch.testing.assert_close(fused_ops.dense_swiglu(gu), torch.nn.functional.silu(gate) * up)
