@@ -7,8 +7,8 @@
 //                           full barrier (plain CTA-local loads).
 //   leader      warp 1      waits for its own stage AND the peer's "stage ready" arrival, issues the pair
 //                           MMAs, commits to both CTAs' empty barriers and both accumulator-full barriers.
-//   peer        warp 1      relay: waits for its own stage, (weight-gradient mode) zero-fills rows past the
-//                           group, then arrives on the leader's peer-ready barrier.
+//   peer        warp 1      weight-gradient mode only: for a tile's ragged last k-block it waits for its own
+//                           loads, zero-fills the rows past the group and forwards the arrival to the leader.
 //   both CTAs   warps 2-5   epilogue of the CTA's own 128 x 256 accumulator half (same code as the
 //                           single-CTA kernel), then arrive on the leader's accumulator-empty barrier.
 //
@@ -64,18 +64,24 @@ __device__ __forceinline__ Tile decode_pair_tile(const GemmParams& p, int t, int
   return tl;
 }
 
-// `bar` is this CTA's own full barrier in the relay scheme (weight-gradient mode) and the LEADER's full barrier
-// otherwise (pair-aware loads credit the leader directly).
+// `bar` is the LEADER's full barrier (pair-aware loads credit the leader directly), except for `direct == false`
+// (the peer's ragged last k-block in the weight-gradient mode): then it is this CTA's own full barrier and the loads
+// are plain ones.
 template <int MODE>
 __device__ __forceinline__ void issue_pair_kblock(const GemmParams& p, const Tile& tl, int kb, int rank,
                                                   const CUtensorMap* map_a, const CUtensorMap* map_b, uint32_t sa,
-                                                  uint32_t sb, uint32_t bar) {
+                                                  uint32_t sb, uint32_t bar, bool direct) {
   using Traits = ModeTraits<MODE>;
   const int chunk0 = tl.n * (kBlockN / 64) + rank * (kBlockN / 128);  // this CTA's half of the 256-wide column tile
   if constexpr (MODE == kModeTgmm) {
-    // relay scheme: plain loads on this CTA's own barrier; A and B are both two 64-column chunks
-    tma_load_3d(sa, map_a, bar, tl.row0 + kb * kBlockK, tl.m * (kBlockM / 64));
-    tma_load_3d(sb, map_b, bar, tl.row0 + kb * kBlockK, chunk0);
+    // A and B are both two 64-column chunks
+    if (direct) {
+      tma_load_3d_pair(sa, map_a, bar, tl.row0 + kb * kBlockK, tl.m * (kBlockM / 64));
+      tma_load_3d_pair(sb, map_b, bar, tl.row0 + kb * kBlockK, chunk0);
+    } else {
+      tma_load_3d(sa, map_a, bar, tl.row0 + kb * kBlockK, tl.m * (kBlockM / 64));
+      tma_load_3d(sb, map_b, bar, tl.row0 + kb * kBlockK, chunk0);
+    }
   } else {
     tma_load_2d_pair(sa, map_a, bar, kb * kBlockK, tl.row0);
     if constexpr (Traits::kBMn) {
@@ -93,8 +99,11 @@ __global__ void __cluster_dims__(2, 1, 1) __maxnreg__(168)
 grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap map_a,
                          const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c) {
   using Traits = ModeTraits<MODE>;
-  // Weight-gradient k-blocks may need rows zeroed by the CTA that owns them, so that mode keeps a CTA-local full
-  // barrier and relays "my half is ready" to the leader; every other mode lets the TMA credit the leader directly.
+  // Every load credits the leader's full barrier directly, with one exception: the last k-block of a weight-gradient
+  // tile whose group does not end on a 64-row boundary needs rows zeroed by the CTA that owns them BEFORE the leader
+  // may use them. For that k-block the peer loads onto its own full barrier, its warp 1 zero-fills and then makes the
+  // arrival on the leader's barrier that the peer's producer makes for every other k-block. (An earlier form relayed
+  // EVERY k-block of that mode through the peer's warp 1: one more hop on the critical path of each stage.)
   constexpr bool kRelay = (MODE == kModeTgmm);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -151,7 +160,8 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; ++s) {
-      mbar_init(full_bar(s), kRelay ? 1 : 2);  // direct scheme: one expect_tx arrival from each CTA of the pair
+      // leader: one arrival from each CTA of the pair; the peer's own barrier only sees its ragged-tail loads
+      mbar_init(full_bar(s), (kRelay && !leader) ? 1 : 2);
       mbar_init(empty_bar(s), 1);
       mbar_init(ready_bar(s), 1);
     }
@@ -184,6 +194,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
   if (warp == 0) {
     // ================================ TMA producer (both CTAs) ==============================
     uint32_t it = 0;
+    uint32_t own_used = 0, own_parity = 0;  // per stage: this CTA's own full barrier has been used / parity of its next use
     int waited_expert = -1;
     long long empty_wait = 0;
     {
@@ -217,11 +228,16 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
             break;
           }
           if (counting) empty_wait += clock64() - w0;
+          const bool own = kRelay && !leader && kb == tl.kblocks - 1 && (tl.nrows % kBlockK) != 0;
+          if (own) {
+            own_used |= 1u << ps;
+            own_parity ^= 1u << ps;
+          }
           if (elect_one()) {
             const uint32_t sa = smem_base + ps * kPairStageBytes;
-            const uint32_t fb = kRelay ? full_bar(ps) : map_to_cta(full_bar(ps), 0);
-            if (kRelay) mbar_expect_tx(fb, kPairStageBytes); else mbar_expect_tx_cluster(fb, kPairStageBytes);
-            issue_pair_kblock<MODE>(p, tl, kb, rank, &map_a, &map_b, sa, sa + kPairStageBytesA, fb);
+            const uint32_t fb = own ? full_bar(ps) : map_to_cta(full_bar(ps), 0);
+            if (own) mbar_expect_tx(fb, kPairStageBytes); else mbar_expect_tx_cluster(fb, kPairStageBytes);
+            issue_pair_kblock<MODE>(p, tl, kb, rank, &map_a, &map_b, sa, sa + kPairStageBytesA, fb, !own);
           }
           ++it;
           if (++ps == kPairStages) { ps = 0; pph ^= 1u; }
@@ -230,11 +246,18 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
       __syncwarp();
     }
     if (counting && lane == 0) prof_add(kProfEmptyWait, empty_wait);
-    if (lane == 0 && *abort_flag && (kRelay || leader)) {
+    // Unwinding: no exit while a copy may still land in this CTA's shared memory. The leader's barriers see every
+    // stage of both CTAs; the peer's own barriers only its ragged-tail loads (their last use has the parity before
+    // the next one's).
+    if (lane == 0 && *abort_flag) {
       for (int s = 0; s < kPairStages; ++s) {
-        if (it > static_cast<uint32_t>(s)) {
-          const uint32_t last = it - 1 - ((it - 1 - s) % kPairStages);
-          mbar_wait(full_bar(s), (last / kPairStages) & 1u, p.mbar_limit);
+        if (leader) {
+          if (it > static_cast<uint32_t>(s)) {
+            const uint32_t last = it - 1 - ((it - 1 - s) % kPairStages);
+            mbar_wait(full_bar(s), (last / kPairStages) & 1u, p.mbar_limit);
+          }
+        } else if ((own_used >> s) & 1u) {
+          mbar_wait(full_bar(s), ((own_parity >> s) & 1u) ^ 1u, p.mbar_limit);
         }
       }
     }
@@ -246,6 +269,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
     constexpr uint32_t kDescStepB = Traits::kBMn ? 2048u : 32u;
     const uint32_t peer = static_cast<uint32_t>(rank ^ 1);
     uint32_t it = 0, tcount = 0;
+    uint32_t own_phase = 0;  // peer, weight-gradient mode: parity of the next use of its own full barrier, per stage
     long long full_wait = 0, acc_wait = 0;
     const long long loop_c0 = counting ? clock64() : 0;
     const uint64_t loop_n0 = counting ? global_timer_ns() : 0;
@@ -299,25 +323,24 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
           tcgen05_fence_after_sync();
         }
         for (int kb = 0; kb < solo_kblocks; ++kb) {
-          const long long w1 = counting ? clock64() : 0;
-          ok = mbar_wait(full_bar(cs), cph, p.mbar_limit, abort_flag);
-          if (ok && kRelay && leader) ok = pair_wait(p.suspend_waits, ready_bar(cs), cph, p.mbar_limit, abort_flag);
-          ok = __all_sync(0xffffffffu, ok);
-          if (counting) full_wait += clock64() - w1;
-          if (!ok) { fail(t, 1300 + cs); break; }
-          if (!leader) {
-            if (elect_one()) mbar_arrive_cluster(map_to_cta(ready_bar(cs), peer));  // this CTA's half is in place
-          } else {
+          if (leader) {
+            const long long w1 = counting ? clock64() : 0;
+            ok = __all_sync(0xffffffffu, mbar_wait(full_bar(cs), cph, p.mbar_limit, abort_flag));
+            if (counting) full_wait += clock64() - w1;
+            if (!ok) { fail(t, 1300 + cs); break; }
             tcgen05_fence_after_sync();
             issue_stage(cs, tmem_d, kBlockK / kUmmaK, kb == 0);
           }
-          advance();
+          advance();  // the peer only keeps count of the stages: its loads credit the leader's barrier
         }
         if (dead) break;
         if constexpr (kRelay) {
           if (ragged_tail) {
             const int kb = tl.kblocks - 1;
-            ok = __all_sync(0xffffffffu, mbar_wait(full_bar(cs), cph, p.mbar_limit, abort_flag));
+            // Leader: both halves have landed and the peer has zero-filled its rows. Peer: its own loads have landed.
+            const uint32_t parity = leader ? cph : ((own_phase >> cs) & 1u);
+            own_phase ^= 1u << cs;
+            ok = __all_sync(0xffffffffu, mbar_wait(full_bar(cs), parity, p.mbar_limit, abort_flag));
             if (!ok) { fail(t, 1300 + cs); break; }
             const int valid = tl.nrows - kb * kBlockK;
             const int ksteps = (valid + kUmmaK - 1) / kUmmaK;
@@ -330,10 +353,9 @@ grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p, const __grid_cons
             fence_proxy_async_smem();
             __syncwarp();
             if (!leader) {
-              if (elect_one()) mbar_arrive_cluster(map_to_cta(ready_bar(cs), peer));
+              // the arrival the peer's producer makes for every other k-block, after the rows are clean
+              if (elect_one()) mbar_arrive_cluster(map_to_cta(full_bar(cs), peer));
             } else {
-              ok = __all_sync(0xffffffffu, pair_wait(p.suspend_waits, ready_bar(cs), cph, p.mbar_limit, abort_flag));
-              if (!ok) { fail(t, 1400 + cs); break; }
               tcgen05_fence_after_sync();
               issue_stage(cs, tmem_d, ksteps, kb == 0);
             }
