@@ -204,7 +204,9 @@ __global__ void __launch_bounds__(256) combine_reduce_kernel(const CombineParams
       for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
       for (int k = 0; k < p.top_k; ++k) {  // fixed k order: bitwise reproducible
         const int pos = p.inv_order[t * p.top_k + k];
-        const int4 raw = *reinterpret_cast<const int4*>(p.rows + static_cast<size_t>(pos) * p.hidden + u * 8);
+        const size_t at = p.blocked ? (static_cast<size_t>(u >> 5) * p.ret_rows + pos) * 256 + (((u & 31) ^ (pos & 7)) << 3)
+                                    : static_cast<size_t>(pos) * p.hidden + u * 8;
+        const int4 raw = *reinterpret_cast<const int4*>(p.rows + at);
         const uint32_t wds[4] = {static_cast<uint32_t>(raw.x), static_cast<uint32_t>(raw.y),
                                  static_cast<uint32_t>(raw.z), static_cast<uint32_t>(raw.w)};
 #pragma unroll

@@ -53,6 +53,8 @@ struct CombineParams {
   const float* dw_rows;       // [T*K] returned d_weight rows (backward) or null
   float* d_weights;           // [T*K] flat by t*K+k (backward) or null
   int num_tokens, top_k, hidden;
+  int blocked, ret_rows;      // `rows` is kept column tile by column tile: [hidden/256][ret_rows][256], 16-byte pieces
+                              // of a row piece XOR-ed with the low three bits of the row number
   const uint32_t* count;      // returned-row counter on this rank
   uint32_t target;            // value the counter reaches when everything is back
   uint32_t spin_limit;

@@ -261,14 +261,22 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
     float w = 1.0f;
     if constexpr (MODE == kModeDownFwd) w = valid ? p.row_w[grow] : 0.0f;
     unsigned long long dst = 0;
+    // Two layouts of the return buffer. Row-major: a row's 512-byte piece of this tile goes to row `pos`, column tile
+    // tl.n. Tile by tile ([column tile][row][256 columns], the 16-byte pieces of a row piece XOR-ed with pos & 7): the
+    // pieces of CONSECUTIVE rows are then contiguous at the destination, and a run of rows of one source segment
+    // leaves as one bulk store of up to 8 KB instead of one store per row (`combine_reduce` undoes the XOR).
+    const bool blocked = p.ret_blocked != 0;
     if (src >= 0)
-      dst = reinterpret_cast<unsigned long long>(p.peer_rows[src] + static_cast<size_t>(pos) * p.ld0 + tl.n * kBlockN);
+      dst = reinterpret_cast<unsigned long long>(
+          blocked ? p.peer_rows[src] + (static_cast<size_t>(tl.n) * p.ret_rows + pos) * kBlockN
+                  : p.peer_rows[src] + static_cast<size_t>(pos) * p.ld0 + tl.n * kBlockN);
+    const int sw = blocked ? (pos & 7) : 0;
     // Rows leave through the async proxy: a lane stages its WHOLE row of the tile (256 columns, 512 bytes) and hands it
     // to the copy engine as one bulk store to the source rank. The warp's staging holds 16 rows, so lanes 0-15 go first
     // and lanes 16-31 follow once the first sixteen stores have read their rows (TMEM is simply read twice). Nobody
     // waits for a remote store: the copy engine keeps the stores of consecutive tiles in flight while the warp goes
     // on to the next accumulator. Row pitch 528 bytes: eight neighbouring lanes hit eight different bank groups.
-    uint8_t* my_row = stage_gen + (lane & 15) * kStageRowPitch;
+    uint8_t* my_row = stage_gen + (lane & 15) * (blocked ? 512 : kStageRowPitch);
     const uint32_t my_row_s = smem_u32(my_row);
 #pragma unroll 1
     for (int pass = 0; pass < 2; ++pass) {
@@ -285,12 +293,12 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
         if (mine) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            *reinterpret_cast<int4*>(my_row + (c * 4 + i) * 16) =
+            *reinterpret_cast<int4*>(my_row + (((c * 4 + i) ^ sw) << 4)) =
                 make_int4(pack_bf16(__uint_as_float(r[8 * i]) * w, __uint_as_float(r[8 * i + 1]) * w),
                           pack_bf16(__uint_as_float(r[8 * i + 2]) * w, __uint_as_float(r[8 * i + 3]) * w),
                           pack_bf16(__uint_as_float(r[8 * i + 4]) * w, __uint_as_float(r[8 * i + 5]) * w),
                           pack_bf16(__uint_as_float(r[8 * i + 6]) * w, __uint_as_float(r[8 * i + 7]) * w));
-            *reinterpret_cast<int4*>(my_row + (c * 4 + 4 + i) * 16) =
+            *reinterpret_cast<int4*>(my_row + (((c * 4 + 4 + i) ^ sw) << 4)) =
                 make_int4(pack_bf16(__uint_as_float(r2[8 * i]) * w, __uint_as_float(r2[8 * i + 1]) * w),
                           pack_bf16(__uint_as_float(r2[8 * i + 2]) * w, __uint_as_float(r2[8 * i + 3]) * w),
                           pack_bf16(__uint_as_float(r2[8 * i + 4]) * w, __uint_as_float(r2[8 * i + 5]) * w),
@@ -298,10 +306,27 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
           }
         }
       }
-      if (mine) {
-        fence_proxy_async_smem();
-        if (dst != 0) bulk_store(dst, my_row_s, 512);
-        bulk_commit();
+      if (!blocked) {
+        if (mine) {
+          fence_proxy_async_smem();
+          if (dst != 0) bulk_store(dst, my_row_s, 512);
+          bulk_commit();
+        }
+      } else {
+        // Runs: consecutive lanes of this pass whose rows go to the same source at consecutive positions. The first
+        // lane of a run stores the whole run (its rows are contiguous in the staging block and at the destination).
+        if (mine) fence_proxy_async_smem();
+        __syncwarp();
+        const int prev_src = __shfl_up_sync(0xffffffffu, src, 1), prev_pos = __shfl_up_sync(0xffffffffu, pos, 1);
+        const bool has = mine && dst != 0;
+        const bool start = has && ((lane & 15) == 0 || prev_src != src || prev_pos + 1 != pos);
+        const uint32_t breaks = __ballot_sync(0xffffffffu, mine && (start || dst == 0));
+        if (start) {
+          const uint32_t after = breaks & ~((2u << lane) - 1u);
+          const int end = after ? (__ffs(after) - 1) : (16 * pass + 16);
+          bulk_store(dst, my_row_s, static_cast<uint32_t>(end - lane) * 512u);
+        }
+        if (mine) bulk_commit();
       }
     }
     if constexpr (MODE == kModeDx) {

@@ -56,6 +56,8 @@ struct GemmParams {
   uint32_t spin_limit;   // polls of a cross-GPU flag before giving up
   uint32_t mbar_limit;   // microseconds a pipeline barrier may take before giving up
   int suspend_waits;     // pair kernels: barriers completed from the partner CTA are waited for with try_wait, not polled
+  int ret_blocked;       // combine modes: the return buffers are kept column tile by column tile (see run_epilogue)
+  int ret_rows;          // rows of a return buffer (the stride between its column tiles in that layout)
   StatusBlock* status;
   // Optional pipeline counters of this mode, [grid][kProfSlots] summed over launches; null = not counted.
   unsigned long long* prof;

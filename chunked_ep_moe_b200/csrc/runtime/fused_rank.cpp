@@ -94,6 +94,7 @@ FusedRank::FusedRank(int P, int L, int me, int S, int D, int F, int K, int strip
   spin_limit_ = static_cast<uint32_t>(spin_limit);
   if (const char* v = std::getenv("CEM_GEMM_EXCLUSIVE_SM")) g_gemm_extra_smem = std::atoi(v) != 0 ? 1024 : 0;
   if (const char* v = std::getenv("CEM_PAIR_SUSPEND")) g_pair_suspend_waits = std::atoi(v) != 0 ? 1 : 0;
+  if (const char* v = std::getenv("CEM_RET_BLOCKED")) ret_blocked_ = std::atoi(v) != 0;
   mbar_limit_ = 20u * 1000u * 1000u;  // microseconds: longer than any legitimate wait on another rank
   lay_ = make_plan_layout(P, L, S, max_slices);
   arena_lay_ = make_arena_layout(P, L, S, D, tk_cap, fp8);
@@ -546,6 +547,8 @@ void FusedRank::compute_forward(int64_t j, torch::Tensor plan, torch::Tensor w_u
     p.b_group_rows = F_;
     p.row_w = reinterpret_cast<const float*>(arena_ + arena_lay_.wbuf) + static_cast<size_t>(b) * S_;
     p.peer_rows = table<__nv_bfloat16>(kTabRet);
+    p.ret_blocked = ret_blocked_ ? 1 : 0;
+    p.ret_rows = tk_cap_;
     p.peer_count = table<uint32_t>(kTabCount);
     p.ld0 = D_;
     launch_gemm(kModeDownFwd, p, map_act_k_[q], weight_map(w_down, 64, cta_pairs_ ? 2 : 4), st);
@@ -650,6 +653,8 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
     p.k_blocks = 2 * F_ / kBlockK;
     p.b_group_rows = D_;
     p.peer_rows = table<__nv_bfloat16>(kTabRet);
+    p.ret_blocked = ret_blocked_ ? 1 : 0;
+    p.ret_rows = tk_cap_;
     p.peer_dw = table<float>(kTabDw);
     p.peer_count = table<uint32_t>(kTabCount);
     p.ld0 = D_;
@@ -702,6 +707,8 @@ void FusedRank::finish_forward(torch::Tensor inv_order, torch::Tensor out) {
   c.num_tokens = static_cast<int>(out.size(0));
   c.top_k = K_;
   c.hidden = D_;
+  c.blocked = ret_blocked_ ? 1 : 0;
+  c.ret_rows = tk_cap_;
   c.count = reinterpret_cast<const uint32_t*>(arena_ + arena_lay_.ret_count);
   c.target = ret_target_;
   c.spin_limit = spin_limit_;
@@ -728,6 +735,8 @@ void FusedRank::finish_backward(torch::Tensor inv_order, torch::Tensor dx, torch
   c.num_tokens = static_cast<int>(dx.size(0));
   c.top_k = K_;
   c.hidden = D_;
+  c.blocked = ret_blocked_ ? 1 : 0;
+  c.ret_rows = tk_cap_;
   c.count = reinterpret_cast<const uint32_t*>(arena_ + arena_lay_.ret_count);
   c.target = ret_target_;
   c.spin_limit = spin_limit_;
