@@ -72,8 +72,26 @@ CASES = [
 
 @pytest.mark.parametrize("group_rows,slice_size,stripe", CASES)
 def test_single_rank_layer_matches_oracle(group_rows, slice_size, stripe):
+    _check_single_rank_case(group_rows, slice_size, stripe)
+
+
+def test_tile_blocked_return_buffers_match_oracle(monkeypatch):
+    """`CEM_RET_BLOCKED=1`: the combine epilogues store runs of rows into return buffers kept column tile by column
+    tile and `combine_reduce` reads that layout; the layer's results must not change."""
+    from chunked_ep_moe_b200.ops import fused
+
+    fused.release_workspaces()  # the switch is read when a workspace's executor is created
+    monkeypatch.setenv("CEM_RET_BLOCKED", "1")
+    try:
+        for group_rows, slice_size, stripe in CASES[:3]:
+            _check_single_rank_case(group_rows, slice_size, stripe, hidden=768)  # three column tiles
+    finally:
+        fused.release_workspaces()
+
+
+def _check_single_rank_case(group_rows, slice_size, stripe, hidden=256):
     gen = torch.Generator().manual_seed(1)
-    E, K, D, F = len(group_rows), 2, 256, 256
+    E, K, D, F = len(group_rows), 2, hidden, 256
     ids = _ids_with_groups(group_rows, K, E, gen)
     T = ids.shape[0]
     x = torch.randn(T, D, generator=gen)
