@@ -270,13 +270,14 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
       dst = reinterpret_cast<unsigned long long>(
           blocked ? p.peer_rows[src] + (static_cast<size_t>(tl.n) * p.ret_rows + pos) * kBlockN
                   : p.peer_rows[src] + static_cast<size_t>(pos) * p.ld0 + tl.n * kBlockN);
-    const int sw = blocked ? (pos & 7) : 0;
+    const bool lsu = p.ret_lsu != 0 && !blocked;
+    const int sw = blocked ? (pos & 7) : (lsu ? (lane & 7) : 0);
     // Rows leave through the async proxy: a lane stages its WHOLE row of the tile (256 columns, 512 bytes) and hands it
     // to the copy engine as one bulk store to the source rank. The warp's staging holds 16 rows, so lanes 0-15 go first
     // and lanes 16-31 follow once the first sixteen stores have read their rows (TMEM is simply read twice). Nobody
     // waits for a remote store: the copy engine keeps the stores of consecutive tiles in flight while the warp goes
     // on to the next accumulator. Row pitch 528 bytes: eight neighbouring lanes hit eight different bank groups.
-    uint8_t* my_row = stage_gen + (lane & 15) * (blocked ? 512 : kStageRowPitch);
+    uint8_t* my_row = stage_gen + (lane & 15) * ((blocked || lsu) ? 512 : kStageRowPitch);
     const uint32_t my_row_s = smem_u32(my_row);
 #pragma unroll 1
     for (int pass = 0; pass < 2; ++pass) {
@@ -306,7 +307,18 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, const Tile& tl
           }
         }
       }
-      if (!blocked) {
+      if (lsu) {
+        // The warp writes the sixteen staged rows out itself, one whole 512-byte row per instruction (lane i moves
+        // piece i): four full lines per store, nothing to wait for before the staging rows are reused.
+        __syncwarp();
+#pragma unroll 4
+        for (int rr = 0; rr < 16; ++rr) {
+          const unsigned long long d = __shfl_sync(0xffffffffu, dst, 16 * pass + rr);
+          const int4 v = *reinterpret_cast<const int4*>(stage_gen + rr * 512 + ((lane ^ (rr & 7)) << 4));
+          if (d != 0) *reinterpret_cast<int4*>(d + static_cast<unsigned long long>(lane) * 16) = v;
+        }
+        __syncwarp();
+      } else if (!blocked) {
         if (mine) {
           fence_proxy_async_smem();
           if (dst != 0) bulk_store(dst, my_row_s, 512);

@@ -58,6 +58,7 @@ struct GemmParams {
   int suspend_waits;     // pair kernels: barriers completed from the partner CTA are waited for with try_wait, not polled
   int ret_blocked;       // combine modes: the return buffers are kept column tile by column tile (see run_epilogue)
   int ret_rows;          // rows of a return buffer (the stride between its column tiles in that layout)
+  int ret_lsu;           // combine modes: staged rows leave with coalesced vector stores instead of bulk stores
   StatusBlock* status;
   // Optional pipeline counters of this mode, [grid][kProfSlots] summed over launches; null = not counted.
   unsigned long long* prof;

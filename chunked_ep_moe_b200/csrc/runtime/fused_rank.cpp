@@ -95,6 +95,7 @@ FusedRank::FusedRank(int P, int L, int me, int S, int D, int F, int K, int strip
   if (const char* v = std::getenv("CEM_GEMM_EXCLUSIVE_SM")) g_gemm_extra_smem = std::atoi(v) != 0 ? 1024 : 0;
   if (const char* v = std::getenv("CEM_PAIR_SUSPEND")) g_pair_suspend_waits = std::atoi(v) != 0 ? 1 : 0;
   if (const char* v = std::getenv("CEM_RET_BLOCKED")) ret_blocked_ = std::atoi(v) != 0;
+  if (const char* v = std::getenv("CEM_RET_LSU")) ret_lsu_ = std::atoi(v) != 0;
   mbar_limit_ = 20u * 1000u * 1000u;  // microseconds: longer than any legitimate wait on another rank
   lay_ = make_plan_layout(P, L, S, max_slices);
   arena_lay_ = make_arena_layout(P, L, S, D, tk_cap, fp8);
@@ -548,6 +549,7 @@ void FusedRank::compute_forward(int64_t j, torch::Tensor plan, torch::Tensor w_u
     p.row_w = reinterpret_cast<const float*>(arena_ + arena_lay_.wbuf) + static_cast<size_t>(b) * S_;
     p.peer_rows = table<__nv_bfloat16>(kTabRet);
     p.ret_blocked = ret_blocked_ ? 1 : 0;
+    p.ret_lsu = ret_lsu_ ? 1 : 0;
     p.ret_rows = tk_cap_;
     p.peer_count = table<uint32_t>(kTabCount);
     p.ld0 = D_;
@@ -654,6 +656,7 @@ void FusedRank::compute_backward(int64_t j, torch::Tensor plan, torch::Tensor w_
     p.b_group_rows = D_;
     p.peer_rows = table<__nv_bfloat16>(kTabRet);
     p.ret_blocked = ret_blocked_ ? 1 : 0;
+    p.ret_lsu = ret_lsu_ ? 1 : 0;
     p.ret_rows = tk_cap_;
     p.peer_dw = table<float>(kTabDw);
     p.peer_count = table<uint32_t>(kTabCount);

@@ -106,6 +106,7 @@ class FusedRank {
   // `cta_pairs_`: the row-wise GEMM modes run as CTA pairs (256-row tiles). `tgmm_pairs_`: the weight-gradient mode
   // does; its pairs split the dense feature dimension, so they cost no token padding and are on by default.
   bool fp8_, use_comm_stream_, cta_pairs_, tgmm_pairs_;
+  bool ret_lsu_ = false;      // CEM_RET_LSU: combine epilogues write staged rows with vector stores, not bulk stores
   bool ret_blocked_ = false;  // CEM_RET_BLOCKED: return buffers kept column tile by column tile (every rank alike)
   uint32_t spin_limit_, mbar_limit_;
   PlanLayout lay_;

@@ -75,13 +75,15 @@ def test_single_rank_layer_matches_oracle(group_rows, slice_size, stripe):
     _check_single_rank_case(group_rows, slice_size, stripe)
 
 
-def test_tile_blocked_return_buffers_match_oracle(monkeypatch):
-    """`CEM_RET_BLOCKED=1`: the combine epilogues store runs of rows into return buffers kept column tile by column
-    tile and `combine_reduce` reads that layout; the layer's results must not change."""
+@pytest.mark.parametrize("switch", ["CEM_RET_BLOCKED", "CEM_RET_LSU"])
+def test_alternative_return_paths_match_oracle(monkeypatch, switch):
+    """The two measurement variants of the combine epilogues must not change the layer's results. `CEM_RET_BLOCKED=1`:
+    runs of rows stored into return buffers kept column tile by column tile, which `combine_reduce` then reads.
+    `CEM_RET_LSU=1`: staged rows written out with coalesced vector stores instead of bulk stores."""
     from chunked_ep_moe_b200.ops import fused
 
-    fused.release_workspaces()  # the switch is read when a workspace's executor is created
-    monkeypatch.setenv("CEM_RET_BLOCKED", "1")
+    fused.release_workspaces()  # the switches are read when a workspace's executor is created
+    monkeypatch.setenv(switch, "1")
     try:
         for group_rows, slice_size, stripe in CASES[:3]:
             _check_single_rank_case(group_rows, slice_size, stripe, hidden=768)  # three column tiles
