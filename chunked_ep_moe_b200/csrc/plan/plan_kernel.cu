@@ -208,10 +208,68 @@ __global__ void __launch_bounds__(256) sort_scan_kernel(int* block_hist, int num
   }
 }
 
+// Stable scatter of one block's 2048 ids. A warp owns 256 CONSECUTIVE ids. (1) every warp counts its ids per expert in
+// shared memory; (2) an exclusive sum over the warps, on top of the block's first slot of each expert, turns the counts
+// into the first output slot of every (warp, expert); (3) each warp walks its ids 32 at a time, in order: lanes holding
+// the same expert find each other with `match.any`, a lane's rank among them is the number of lower lanes, and the
+// lowest lane advances the (warp, expert) slot. (The serial form below took 45 us per launch on the critical path at
+// the start of every pass; this one a few.)
+constexpr int kSortWarps = kSortThreads / 32;
+constexpr int kSortRankedMaxExperts = 1024;  // kSortWarps * experts ints of shared memory: 32 KB
+
 __global__ void __launch_bounds__(kSortThreads) sort_scatter_kernel(const int* ids, int n, int num_experts,
                                                                   const int* block_off, int* order, int* inv_order) {
-  // Stable inside the block: a thread owns kSortItems CONSECUTIVE ids; ranks come from a per-expert
-  // scan over threads (done expert by expert with ballots over the ids each thread holds).
+  extern __shared__ int s_slot[];  // [kSortWarps][num_experts]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int base = blockIdx.x * kSortThreads * kSortItems + warp * (kSortItems * 32);
+  for (int i = threadIdx.x; i < kSortWarps * num_experts; i += blockDim.x) s_slot[i] = 0;
+  __syncthreads();
+  int* mine = s_slot + warp * num_experts;
+  int e_of[kSortItems];
+#pragma unroll
+  for (int g = 0; g < kSortItems; ++g) {
+    const int idx = base + g * 32 + lane;
+    int e = (idx < n) ? ids[idx] : -1;
+    if (e < 0 || e >= num_experts) e = -1;  // takes no part in the sort
+    e_of[g] = e;
+    if (e >= 0) atomicAdd(mine + e, 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+    int run = block_off[e * gridDim.x + blockIdx.x];
+#pragma unroll
+    for (int w = 0; w < kSortWarps; ++w) {
+      const int c = s_slot[w * num_experts + e];
+      s_slot[w * num_experts + e] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int g = 0; g < kSortItems; ++g) {
+    const int e = e_of[g];
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int leader = __ffs(peers) - 1;
+    int first = 0;
+    if (e >= 0 && lane == leader) {
+      first = mine[e];
+      mine[e] = first + __popc(peers);
+    }
+    first = __shfl_sync(0xffffffffu, first, leader);
+    if (e >= 0) {
+      const int slot = first + __popc(peers & ((1u << lane) - 1u));
+      const int idx = base + g * 32 + lane;
+      order[slot] = idx;
+      inv_order[idx] = slot;
+    }
+    __syncwarp();  // the next group's leaders see this group's slot updates
+  }
+}
+
+__global__ void __launch_bounds__(kSortThreads) sort_scatter_serial_kernel(const int* ids, int n, int num_experts,
+                                                                  const int* block_off, int* order, int* inv_order) {
+  // Fallback for more experts than the ranked kernel below has shared memory for: one thread per expert walks the
+  // block's ids in order.
   extern __shared__ int s_mem[];
   int* s_next = s_mem;                       // [num_experts] next output slot per expert
   int* s_ids = s_mem + num_experts;          // [kSortThreads * kSortItems]
@@ -260,8 +318,12 @@ void launch_expert_sort(const int* expert_ids, int n, int num_experts, int* orde
   sort_hist_kernel<<<blocks, kSortThreads, num_experts * sizeof(int), stream>>>(expert_ids, n, num_experts, scratch,
                                                                                 status);
   sort_scan_kernel<<<1, 256, 0, stream>>>(scratch, num_experts, blocks, counts);
-  sort_scatter_kernel<<<blocks, kSortThreads, (num_experts + kSortThreads * kSortItems) * sizeof(int), stream>>>(
-      expert_ids, n, num_experts, scratch, order, inv_order);
+  if (num_experts <= kSortRankedMaxExperts)
+    sort_scatter_kernel<<<blocks, kSortThreads, kSortWarps * num_experts * sizeof(int), stream>>>(
+        expert_ids, n, num_experts, scratch, order, inv_order);
+  else
+    sort_scatter_serial_kernel<<<blocks, kSortThreads, (num_experts + kSortThreads * kSortItems) * sizeof(int),
+                                 stream>>>(expert_ids, n, num_experts, scratch, order, inv_order);
 }
 
 }  // namespace cem
