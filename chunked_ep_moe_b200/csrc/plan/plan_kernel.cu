@@ -19,6 +19,69 @@ __device__ __forceinline__ int warp_exclusive_scan(int v, int lane, int* total) 
   return inc - v;
 }
 
+// Per-pass sums on the device (what `plan_phase_a` computes with one loop nest per value): every sum the tables need is
+// a prefix of a row of the traffic matrix or of the per-receiver expert totals, so the block first builds those prefix
+// tables in shared memory (one thread per row, 2 P + 1 rows of at most P * L values), then every value is a lookup plus
+// at most P additions. `rowsum[r][l]`: rows expert l of rank r receives; `ebegin[r][l]`: where they start in r's stream;
+// `prefix[s][q]`: copies of source s that sort before its q-th (receiver, expert) pair.
+__device__ void plan_phase_a_block(const int* counts, int* plan, const PlanLayout& y, int me, int* rowsum, int* ebegin,
+                                   int* prefix) {
+  const int P = y.P, L = y.L, n = P * L;
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  for (int i = tid; i < n; i += nthreads) {
+    int sum = 0;
+    for (int s = 0; s < P; ++s) sum += counts[s * n + i];
+    rowsum[i] = sum;
+  }
+  __syncthreads();
+  for (int row = tid; row < 2 * P; row += nthreads) {
+    if (row < P) {  // exclusive scan of one receiver's expert totals
+      int run = 0;
+      for (int l = 0; l < L; ++l) { ebegin[row * L + l] = run; run += rowsum[row * L + l]; }
+    } else {        // exclusive scan of one source's row of the traffic matrix
+      const int s = row - P;
+      int run = 0;
+      for (int q = 0; q < n; ++q) { prefix[s * n + q] = run; run += counts[s * n + q]; }
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < n; i += nthreads) {
+    const int a = i / L, l = i - a * L;  // a is the receiver r (sender view) or the source s (receiver view)
+    int seg_start = ebegin[a * L + l];
+    for (int s = 0; s < me; ++s) seg_start += counts[s * n + a * L + l];
+    int in_start = ebegin[me * L + l];
+    for (int s = 0; s < a; ++s) in_start += counts[s * n + me * L + l];
+    plan[y.off_send_start + i] = prefix[me * n + i];
+    plan[y.off_seg_start + i] = seg_start;
+    plan[y.off_seg_size + i] = counts[me * n + i];
+    plan[y.off_in_start + i] = in_start;
+    plan[y.off_in_size + i] = counts[a * n + me * L + l];
+    plan[y.off_src_send_start + i] = prefix[a * n + me * L + l];
+  }
+  for (int l = tid; l < L; l += nthreads) {
+    plan[y.off_expert_start + l] = ebegin[me * L + l];
+    plan[y.off_expert_rows + l] = rowsum[me * L + l];
+  }
+  if (tid == 0) {
+    int max_rows = 0, my_rows = 0;
+    for (int r = 0; r < P; ++r) {
+      const int rows = ebegin[r * L + L - 1] + rowsum[r * L + L - 1];
+      if (rows > max_rows) max_rows = rows;
+      if (r == me) my_rows = rows;
+    }
+    const int my_copies = prefix[me * n + n - 1] + counts[me * n + n - 1];
+    const int local_end = (me + 1) * L < n ? prefix[me * n + (me + 1) * L] : my_copies;
+    const int num_slices = (max_rows + y.S - 1) / y.S;
+    plan[0] = num_slices;
+    plan[1] = my_rows;
+    plan[2] = max_rows;
+    plan[3] = my_copies - (local_end - prefix[me * n + me * L]);  // copies that leave this rank
+    plan[4] = num_slices > y.max_slices ? 1 : 0;
+    plan[5] = my_copies;
+    for (int q = 6; q < kPlanHeaderInts; ++q) plan[q] = 0;
+  }
+}
+
 // Per-slice tables, one warp per slice (what `plan_phase_b` does with one thread per slice): lanes take the experts
 // (then the segments) 32 at a time and a warp scan numbers their tiles (their put chunks) in expert order.
 __device__ void plan_phase_b_warps(int* plan, const PlanLayout& y, const int* seg_start, const int* seg_size,
@@ -130,7 +193,8 @@ __global__ void __launch_bounds__(256) plan_build_kernel(const PlanKernelParams 
     int* s_counts = s_plan;
     for (int i = threadIdx.x; i < P * n; i += blockDim.x) s_counts[i] = p.counts[i];
     __syncthreads();
-    plan_phase_a(s_counts, p.plan, p.lay, p.me, threadIdx.x, blockDim.x);
+    // scratch of the per-pass sums: rowsum [n], ebegin [n], prefix [P * n]; the same space holds phase B's inputs after
+    plan_phase_a_block(s_counts, p.plan, p.lay, p.me, s_counts + P * n, s_counts + P * n + n, s_counts + P * n + 2 * n);
     __syncthreads();
     int* s_seg_start = s_counts + P * n;
     int* s_seg_size = s_seg_start + n;
@@ -296,8 +360,10 @@ __global__ void __launch_bounds__(kSortThreads) sort_scatter_serial_kernel(const
 void launch_plan_build(const PlanKernelParams& p_in, cudaStream_t stream) {
   PlanKernelParams p = p_in;
   const int n = p.lay.P * p.lay.L;
-  const size_t smem = sizeof(int) * (static_cast<size_t>(p.lay.P) * n + 3 * static_cast<size_t>(n) + 2 * p.lay.L);
-  p.use_smem = smem <= 40 * 1024 ? 1 : 0;  // 256 experts on 8 ranks need 11.5 KB; anything larger takes the serial path
+  // the matrix [P * n], then the larger of phase A's scratch (2 n + P * n) and phase B's inputs (3 n + 2 L)
+  const size_t after = static_cast<size_t>(p.lay.P) * n + 2 * static_cast<size_t>(n) + 2 * p.lay.L + n;
+  const size_t smem = sizeof(int) * (static_cast<size_t>(p.lay.P) * n + after);
+  p.use_smem = smem <= 40 * 1024 ? 1 : 0;  // 256 experts on 8 ranks need 20 KB; anything larger takes the serial path
   plan_build_kernel<<<1, 256, p.use_smem ? smem : 0, stream>>>(p);
 }
 
